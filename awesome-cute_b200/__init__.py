@@ -1,0 +1,11 @@
+"""B200 (sm_100a) W4A16 GEMM: drop-in for the Marlin path of CalebDu/Awesome-Cute (gemm/marlin_gemm).
+
+The directory name carries a hyphen, so load it through ``__graft_entry__.load_package()`` (or
+importlib) under the module name ``awesome_cute_b200``.
+"""
+from . import _lib  # raises if libw4a16.so is not built: there is no fallback
+from .marlin import (Layer, device_status, mul, mul_simt, pack_weights, permute_scales, quantize_pack,
+                     shard_columns, unpack_weights, unpermute_scales)
+
+__all__ = ["Layer", "mul", "mul_simt", "device_status", "pack_weights", "unpack_weights", "permute_scales",
+           "unpermute_scales", "quantize_pack", "shard_columns"]

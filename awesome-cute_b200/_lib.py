@@ -1,0 +1,50 @@
+"""ctypes door onto libw4a16.so (the C ABI declared in include/w4a16.h).
+
+There is no Python or CPU implementation behind this module: if the shared library has not been
+built (``python -c "import __graft_entry__ as g; g.build()"`` or ``make -C awesome-cute_b200/csrc``)
+importing it raises.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libw4a16.so")
+
+OK, ERR_PROB_SHAPE, ERR_KERN_SHAPE, ERR_CUDA, ERR_TIMEOUT, ERR_ARG = 0, 1, 2, 3, 4, 5
+
+# every symbol include/w4a16.h declares: name -> (restype, argtypes)
+_vp, _i = ctypes.c_void_p, ctypes.c_int
+_GEMM_ARGS = [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i]
+SYMBOLS = {
+    "w4a16_marlin_gemm": (_i, _GEMM_ARGS),
+    "w4a16_marlin_gemm_simt": (_i, _GEMM_ARGS),
+    "w4a16_workspace_ints": (_i, [_i, _i]),
+    "w4a16_device_status": (_i, [_i, _vp]),
+    "w4a16_last_cuda_error": (ctypes.c_char_p, []),
+    "w4a16_pack_weights": (_i, [_vp, _i, _i, _vp]),
+    "w4a16_unpack_weights": (_i, [_vp, _i, _i, _vp]),
+    "w4a16_permute_scales": (_i, [_vp, _i, _i, _vp]),
+    "w4a16_unpermute_scales": (_i, [_vp, _i, _i, _vp]),
+    "w4a16_quantize_pack": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
+    "w4a16_shard_columns": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
+}
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "libw4a16.so is not built (%s). Build it with `make -C awesome-cute_b200/csrc`; "
+            "there is no fallback implementation." % LIB_PATH)
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)  # AttributeError here means the library does not match the header
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def last_cuda_error():
+    return lib.w4a16_last_cuda_error().decode()

@@ -1,0 +1,328 @@
+// Host launcher + C ABI of the sm_100a W4A16 GEMM (declarations: include/w4a16.h, include/marlin_cute.h).
+//
+// Takes the place of the reference's launcher marlin_cute (gemm/marlin_gemm/marlin_cute_kernel.cu:28-115):
+// same arguments, same shape checks and return codes, but ONE launch for any m (the reference loops
+// over 64-row chunks and re-streams the weights per chunk, :71-111), tensor maps instead of raw pointer
+// arithmetic, and per-(device, stream) cached state instead of per-call attribute queries (:18,35,38).
+// There is no CPU path and no fallback: if the device is not sm_100 the launch fails with a CUDA error.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <string>
+#include <utility>
+
+#include "../../include/marlin_cute.h"
+#include "../../include/w4a16.h"
+#include "w4a16_kernel.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+bool cuda_ok(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return true;
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return false;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, fetched through the runtime so the library needs no link against libcuda.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void *f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+bool encode(CUtensorMap *map, CUtensorMapDataType dt, int rank, const void *base, const cuuint64_t *dims,
+            const cuuint64_t *strides_bytes, const cuuint32_t *box, CUtensorMapSwizzle swz, const char *what) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    g_last_error = "cuTensorMapEncodeTiled entry point not available";
+    return false;
+  }
+  const cuuint32_t ones[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void *>(base), dims, strides_bytes, box, ones,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_error = std::string("cuTensorMapEncodeTiled(") + what + ") failed with CUresult " + std::to_string((int)r);
+    return false;
+  }
+  return true;
+}
+
+// Per (device, stream) state: scratch of the stream-K fix-up, the status word, the launch epoch.
+struct StreamCtx {
+  float *partials = nullptr;
+  size_t partial_floats = 0;
+  uint32_t *flags = nullptr;  // [MAX_GRID][4]
+  int *status = nullptr;
+  uint32_t epoch = 0;
+};
+constexpr int MAX_GRID = 256;
+
+std::mutex g_mu;
+std::map<std::pair<int, cudaStream_t>, StreamCtx> g_ctx;
+int g_sm_count[64] = {0};
+
+int sm_count(int dev) {
+  if (dev < 0 || dev >= 64) return -1;
+  if (g_sm_count[dev] == 0) {
+    int v = 0;
+    if (!cuda_ok(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute")) return -1;
+    g_sm_count[dev] = v;
+  }
+  return g_sm_count[dev];
+}
+
+// Must be called with g_mu held.  Grows the partial-tile scratch when a launch needs more.
+StreamCtx *get_ctx(int dev, cudaStream_t stream, size_t need_floats) {
+  StreamCtx &c = g_ctx[{dev, stream}];
+  if (!c.flags) {
+    if (!cuda_ok(cudaMalloc(&c.flags, sizeof(uint32_t) * 4 * MAX_GRID), "cudaMalloc(flags)")) return nullptr;
+    if (!cuda_ok(cudaMalloc(&c.status, sizeof(int)), "cudaMalloc(status)")) return nullptr;
+    if (!cuda_ok(cudaMemset(c.flags, 0, sizeof(uint32_t) * 4 * MAX_GRID), "cudaMemset(flags)")) return nullptr;
+    if (!cuda_ok(cudaMemset(c.status, 0, sizeof(int)), "cudaMemset(status)")) return nullptr;
+  }
+  if (c.partial_floats < need_floats) {
+    if (c.partials) {
+      if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return nullptr;
+      cudaFree(c.partials);
+      c.partials = nullptr;
+      c.partial_floats = 0;
+    }
+    if (!cuda_ok(cudaMalloc(&c.partials, sizeof(float) * need_floats), "cudaMalloc(partials)")) return nullptr;
+    c.partial_floats = need_floats;
+  }
+  return &c;
+}
+
+struct Problem {
+  const void *A, *B, *s;
+  void *C;
+  int m, n, k, groupsize, dev, sms;
+  cudaStream_t stream;
+};
+
+template <int TM, int KS, bool GROUPED>
+int launch_tc(const Problem &pr) {
+  using Cfg = w4a16::Config<TM, KS>;
+  auto kern = w4a16::w4a16_tc_kernel<TM, KS, GROUPED>;
+  // at least 116 KiB so that two CTAs can never share an SM (each one allocates all of TMEM)
+  constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
+  static bool attr_done[64] = {false};
+
+  const int nsm = sm_count(pr.dev);
+  if (nsm <= 0) return W4A16_ERR_CUDA;
+
+  w4a16::Params p{};
+  p.m = pr.m, p.n = pr.n, p.k = pr.k;
+  p.n_tiles = pr.n / w4a16::TILE_N;
+  p.m_tiles = (pr.m + TM - 1) / TM;
+  p.k_iters = pr.k / KS;
+  const long total = (long)p.n_tiles * p.m_tiles * p.k_iters;
+  if (total > 0x7fffffffL) return W4A16_ERR_ARG;
+  p.total_iters = (int)total;
+  int grid = pr.sms > 0 ? pr.sms : nsm;
+  if (grid > nsm) grid = nsm;  // the finisher of a split tile needs its contributors co-resident
+  if (grid > MAX_GRID) grid = MAX_GRID;
+  if (grid > p.total_iters) grid = p.total_iters;
+  p.iters_per_cta = (p.total_iters + grid - 1) / grid;
+  grid = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
+  p.s = static_cast<const __half *>(pr.s);
+  p.C = static_cast<__half *>(pr.C);
+
+  CUtensorMap tmB, tmA, tmS;
+  {  // weights: int32 [k/16][2n] viewed as [k/16][2n/32][32] so a 128-byte inner box can be swizzled
+    const cuuint64_t dims[3] = {32, (cuuint64_t)(2 * pr.n / 32), (cuuint64_t)(pr.k / 16)};
+    const cuuint64_t strides[2] = {128, (cuuint64_t)pr.n * 8};
+    const cuuint32_t box[3] = {32, 8, (cuuint32_t)(KS / 16)};
+    if (!encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, pr.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B"))
+      return W4A16_ERR_CUDA;
+  }
+  {  // activations: fp16 [m][k]; rows past m read as zero
+    const cuuint64_t dims[2] = {(cuuint64_t)pr.k, (cuuint64_t)pr.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)pr.k * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)TM};
+    if (!encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A"))
+      return W4A16_ERR_CUDA;
+  }
+  if (GROUPED) {  // scales: fp16 [k/128][n]
+    const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
+    const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, 1};
+    if (!encode(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
+      return W4A16_ERR_CUDA;
+  } else {
+    tmS = tmA;  // never read
+  }
+
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!attr_done[pr.dev]) {
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"))
+      return W4A16_ERR_CUDA;
+    attr_done[pr.dev] = true;
+  }
+  StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 128 * w4a16::TILE_N);
+  if (!ctx) return W4A16_ERR_CUDA;
+  if (++ctx->epoch == 0) ctx->epoch = 1;
+  p.partials = ctx->partials;
+  p.flags = ctx->flags;
+  p.status = ctx->status;
+  p.epoch = ctx->epoch;
+  kern<<<grid, Cfg::THREADS, smem, pr.stream>>>(tmB, tmA, tmS, p);
+  if (!cuda_ok(cudaGetLastError(), "kernel launch")) return W4A16_ERR_CUDA;
+  return W4A16_OK;
+}
+
+template <int TM, int KS>
+int launch_tc_g(const Problem &pr) {
+  return pr.groupsize == 128 ? launch_tc<TM, KS, true>(pr) : launch_tc<TM, KS, false>(pr);
+}
+
+int dispatch_tc(const Problem &pr) {
+  // batch tile = UMMA N; deep 128-k stages while the activation tile is small
+  const bool k128 = (pr.k % 128) == 0;
+  if (pr.m <= 16) return k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
+  if (pr.m <= 32) return k128 ? launch_tc_g<32, 128>(pr) : launch_tc_g<32, 64>(pr);
+  if (pr.m <= 64) return k128 ? launch_tc_g<64, 128>(pr) : launch_tc_g<64, 64>(pr);
+  return launch_tc_g<128, 64>(pr);
+}
+
+// ---- diagnostic CUDA-core kernel: one thread per output, closed form of the packed layout
+__global__ void w4a16_simt_kernel(const __half *A, const uint32_t *B, __half *C, const __half *s, int m, int n, int k,
+                                  int groupsize) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)m * n) return;
+  const int mm = (int)(idx / n), nn = (int)(idx % n);
+  const int nr = nn % 64, j = nr / 16, hi = (nr % 16) / 8;
+  const long cbase = 128L * (nn / 64) + j;
+  float acc = 0.f;
+  for (int kk = 0; kk < k; ++kk) {
+    const int kr = kk % 16;
+    const int lane = 4 * (nr % 8) + (kr % 8) / 2;
+    const int nib = 4 * (kr % 2) + 2 * hi + kr / 8;
+    const int code = (int)((B[(long)(kk / 16) * 2 * n + cbase + 4 * lane] >> (4 * nib)) & 0xfu);
+    __half w = __int2half_rn(code - 8);
+    if (groupsize != -1) w = __hmul(w, s[(long)(kk / groupsize) * n + 64 * (nn / 64) + 8 * (nr % 8) + nr / 8]);
+    acc += __half2float(A[(long)mm * k + kk]) * __half2float(w);
+  }
+  __half h = __float2half(acc);
+  if (groupsize == -1) {
+    const int c32 = nn % 32;
+    h = __hmul(h, s[nn - c32 + 8 * ((c32 % 8) / 2) + 2 * (c32 / 8) + c32 % 2]);
+  }
+  C[idx] = h;
+}
+
+int launch_simt(const Problem &pr) {
+  const long total = (long)pr.m * pr.n;
+  const int threads = 256;
+  const long blocks = (total + threads - 1) / threads;
+  if (blocks > 0x7fffffffL) return W4A16_ERR_ARG;
+  w4a16_simt_kernel<<<(unsigned)blocks, threads, 0, pr.stream>>>(
+      static_cast<const __half *>(pr.A), static_cast<const uint32_t *>(pr.B), static_cast<__half *>(pr.C),
+      static_cast<const __half *>(pr.s), pr.m, pr.n, pr.k, pr.groupsize);
+  if (!cuda_ok(cudaGetLastError(), "kernel launch")) return W4A16_ERR_CUDA;
+  return W4A16_OK;
+}
+
+// Shape / dispatch checks with the reference's meaning and order (marlin_cute_kernel.cu:39-60,95-107).
+int check_problem(int prob_m, int prob_n, int prob_k, int groupsize, int &thread_k, int &thread_n) {
+  if (thread_k == -1 || thread_n == -1) {
+    if (prob_m <= 16) {
+      thread_k = 128, thread_n = 128;
+    } else {
+      thread_k = 64, thread_n = 256;
+    }
+  }
+  if (thread_k <= 0 || thread_n <= 0) return W4A16_ERR_KERN_SHAPE;
+  const int group_blocks = groupsize == -1 ? -1 : groupsize / 16;
+  if (prob_n % thread_n != 0 || prob_k % thread_k != 0 || (group_blocks > 0 && prob_k % group_blocks != 0))
+    return W4A16_ERR_PROB_SHAPE;
+  if (prob_m == 0 || prob_n == 0 || prob_k == 0) return -1;  // nothing to do
+  // the reference instantiates (thread_n, thread_k) = (128,128) for one 16-row block only and (256,64) for
+  // one to four blocks per launch chunk, group size 128 or -1
+  const bool t128 = (thread_n == 128 && thread_k == 128), t256 = (thread_n == 256 && thread_k == 64);
+  if (!(t128 || t256)) return W4A16_ERR_KERN_SHAPE;
+  if (t128 && prob_m > 16) return W4A16_ERR_KERN_SHAPE;
+  if (groupsize != -1 && groupsize != 128) return W4A16_ERR_KERN_SHAPE;
+  return W4A16_OK;
+}
+
+int gemm_entry(bool simt, const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n, int prob_k,
+               void *workspace, int groupsize, int dev, cudaStream_t stream, int thread_k, int thread_n, int sms,
+               int max_par) {
+  (void)max_par;
+  (void)workspace;  // the caller's lock array is not needed by this kernel and is left untouched (all zero)
+  if (prob_m < 0 || prob_n < 0 || prob_k < 0) return W4A16_ERR_ARG;
+  const int chk = check_problem(prob_m, prob_n, prob_k, groupsize, thread_k, thread_n);
+  if (chk == -1) return W4A16_OK;
+  if (chk != W4A16_OK) return chk;
+  if (!A || !B || !C || !s) return W4A16_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(s)) & 15)
+    return W4A16_ERR_ARG;
+  if (dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  Problem pr{A, B, s, C, prob_m, prob_n, prob_k, groupsize, dev, sms, stream};
+  return simt ? launch_simt(pr) : dispatch_tc(pr);
+}
+
+}  // namespace
+
+int marlin_cute(const void *A, const void *B, void *C, void *s, int prob_m, int prob_n, int prob_k, void *workspace,
+                int groupsize, int dev, cudaStream_t stream, int thread_k, int thread_n, int sms, int max_par) {
+  return gemm_entry(false, A, B, C, s, prob_m, prob_n, prob_k, workspace, groupsize, dev, stream, thread_k, thread_n,
+                    sms, max_par);
+}
+
+extern "C" int w4a16_marlin_gemm(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n,
+                                 int prob_k, void *workspace, int groupsize, int dev, void *stream, int thread_k,
+                                 int thread_n, int sms, int max_par) {
+  return gemm_entry(false, A, B, C, s, prob_m, prob_n, prob_k, workspace, groupsize, dev,
+                    static_cast<cudaStream_t>(stream), thread_k, thread_n, sms, max_par);
+}
+
+extern "C" int w4a16_marlin_gemm_simt(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n,
+                                      int prob_k, void *workspace, int groupsize, int dev, void *stream, int thread_k,
+                                      int thread_n, int sms, int max_par) {
+  return gemm_entry(true, A, B, C, s, prob_m, prob_n, prob_k, workspace, groupsize, dev,
+                    static_cast<cudaStream_t>(stream), thread_k, thread_n, sms, max_par);
+}
+
+extern "C" int w4a16_workspace_ints(int prob_n, int max_par) {
+  if (prob_n < 0 || max_par < 0) return 0;
+  return prob_n / 128 * max_par;
+}
+
+extern "C" int w4a16_device_status(int dev, void *stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return W4A16_ERR_CUDA;
+  int *status = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_ctx.find({dev, st});
+    if (it == g_ctx.end()) return W4A16_OK;  // nothing was ever launched here
+    status = it->second.status;
+  }
+  int word = 0;
+  if (!cuda_ok(cudaMemcpy(&word, status, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy(status)")) return W4A16_ERR_CUDA;
+  if (word == 0) return W4A16_OK;
+  if (!cuda_ok(cudaMemset(status, 0, sizeof(int)), "cudaMemset(status)")) return W4A16_ERR_CUDA;
+  g_last_error = "device-side wait timed out at site " + std::to_string(word >> 8);
+  return W4A16_ERR_TIMEOUT;
+}
+
+extern "C" const char *w4a16_last_cuda_error(void) { return g_last_error.c_str(); }

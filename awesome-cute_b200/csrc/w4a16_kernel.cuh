@@ -1,0 +1,379 @@
+// The sm_100a W4A16 GEMM kernel:  C[m,n] (fp16) = A[m,k] (fp16) x dequant(B, s)[k,n],  fp32 accumulation.
+//
+// It takes the place of the reference's MarlinGemmTraits::operator()
+// (gemm/marlin_gemm/marlin_cute_trait.h:306-970: cp.async ring, ldmatrix, mma.sync.m16n8k16, serial
+// in-place fp16 fix-up) and reads the same operands, bit for bit.  Nothing of its structure is kept.
+//
+// Formulation.  The problem is run transposed, D[n, m] = sum_k W[n, k] * A[m, k], so that
+//   * the 128 weight columns of a tile are the 128 rows (TMEM lanes) of a tcgen05.mma with M = 128,
+//   * the batch tile (TM = 16 .. 128 rows of A) is the UMMA N dimension, read K-major straight from
+//     the shared-memory tile TMA wrote (128-byte swizzle),
+//   * the dequantised weights are the UMMA *A* operand and live in TENSOR MEMORY: each dequant thread
+//     owns one weight column, turns its packed nibbles into fp16 pairs in registers and writes them
+//     with one tcgen05.st per k-step; they never pass through shared memory as fp16.
+// A packed word holds two columns (n, n+8) x four k (2t, 2t+1, 2t+8, 2t+9); the thread owning column n
+// uses the word as it is and the thread owning n+8 uses word >> 8, so every nibble is converted once.
+// k-pair (2t, 2t+1) lands in TMEM column t of its 16-k block and (2t+8, 2t+9) in column 4+t, which is
+// natural k order, the order of the activation tile.
+//
+// Warp roles (one CTA per SM, persistent):
+//   warps [0, NDQ)        dequant: smem nibbles -> registers -> TMEM operand ring      (NDQ = 4 or 8)
+//   warps [NDQ, NDQ+4)    epilogue: TMEM accumulator -> fix-up -> fp16 -> C
+//   warp  NDQ+4           TMA producer (one lane)
+//   warp  NDQ+5           tcgen05.mma issuer (one lane); also owns the TMEM allocation
+// Hand-offs are mbarriers; the accumulator is double buffered in TMEM so the epilogue of one tile
+// overlaps the main loop of the next.
+//
+// Work split: stream-K.  The (tile, k-step) space is linearised tile-major, n fastest
+// (marlin_cute_trait.h:278-286 uses the same order) and cut into equal contiguous ranges, one per CTA.
+// A tile cut between CTAs is finished by the CTA that holds its k-step 0; the others store their fp32
+// partial tile to library-owned scratch and publish a per-CTA flag (release) carrying the launch epoch.
+// The finisher reaches that tile LAST in its own range while the contributors reach it FIRST in theirs,
+// so in practice it never waits; contributors never wait at all (no serial chain as in
+// marlin_cute_trait.h:935-950).  The finisher's wait is bounded like every other wait in the kernel.
+#pragma once
+#include "ptx_sm100.cuh"
+
+namespace w4a16 {
+
+constexpr int TILE_N = 128;                         // weight columns per tile = UMMA M
+constexpr int EPI_WARPS = 4;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
+constexpr int STATUS_TIMEOUT = 4;                   // == W4A16_ERR_TIMEOUT
+
+struct Params {
+  int m, n, k;
+  int n_tiles, m_tiles, k_iters;        // k_iters = k / KS
+  int total_iters, iters_per_cta;
+  const __half *s;                      // scales (read directly by the epilogue when per-channel)
+  __half *C;
+  float *partials;                      // [gridDim.x][TM][128] fp32 partial tiles (stream-K fix-up)
+  uint32_t *flags;                      // [gridDim.x][4] epoch flags, one per epilogue warp
+  uint32_t epoch;                       // this launch's number (never 0)
+  int *status;                          // 0, or STATUS_TIMEOUT | (site << 8)
+};
+
+template <int TM, int KS>
+struct Config {
+  static_assert(TM == 16 || TM == 32 || TM == 64 || TM == 128, "batch tile");
+  static_assert(KS == 64 || KS == 128, "k per stage");
+  static constexpr int W_BYTES = KS * TILE_N / 2;            // packed weights per stage
+  static constexpr int A_BYTES = TM * KS * 2;                // activations per stage (KS/64 boxes of TM x 128 B)
+  static constexpr int S_BYTES = TILE_N * 2;                 // one row of group scales
+  static constexpr int STAGE_BYTES = W_BYTES + A_BYTES + S_BYTES;
+  static constexpr int WBUFS = 4;                            // TMEM operand ring depth
+  static constexpr int WBUF_COLS = KS / 2;                   // fp16 pairs per lane per stage
+  static constexpr int ACC_STRIDE = TM < 32 ? 32 : TM;       // TMEM columns between the two accumulators
+  static constexpr int WBUF_COL0 = 2 * ACC_STRIDE;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(WBUF_COL0 + WBUFS * WBUF_COLS <= TMEM_COLS, "TMEM budget");
+  static constexpr int SMEM_BUDGET = 200 * 1024;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
+  static_assert(STAGES >= 3, "ring too shallow");
+  static constexpr int NDQ = TM <= 32 ? 8 : 4;               // dequant warps
+  static constexpr int NDQ_SETS = NDQ / 4;
+  static constexpr int THREADS = (NDQ + EPI_WARPS + 2) * 32;
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int SMEM_BYTES = STAGES * (W_BYTES + A_BYTES) + STAGES * S_BYTES + BAR_BYTES + 1024 /*align slack*/;
+};
+
+struct Bars {  // lives in shared memory
+  uint64_t full[12];
+  uint64_t empty[12];
+  uint64_t wfull[4];
+  uint64_t wempty[4];
+  uint64_t accfull[2];
+  uint64_t accempty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort;
+};
+static_assert(sizeof(Bars) <= 1024, "barrier block");
+
+// A wait whose verdict is the same in every lane of the warp (the tcgen05 ld/st that follow are
+// warp-collective), recording the site on failure.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *abort) {
+  const bool ok = sm100::mbar_wait(bar, parity, abort, WAIT_LIMIT_NS);
+  return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ void give_up(const Params &p, volatile int *abort, int site) {
+  *abort = 1;
+  atomicCAS(p.status, 0, STATUS_TIMEOUT | (site << 8));
+}
+
+// int4 -> fp16 exactly (zero point 8), two weights per instruction, as in the reference's dequant
+// (marlin_cute_trait.h:8-39): OR the nibble into the mantissa of 1024.0 and subtract 1032; the high
+// nibbles carry a factor 16 folded into one fma.
+__device__ __forceinline__ void dequant_word(uint32_t w, __half2 scale, uint32_t &lo, uint32_t &hi) {
+  const uint32_t l = sm100::lop3_and_or(w, 0x000f000fu, 0x64006400u);
+  const uint32_t h = sm100::lop3_and_or(w, 0x00f000f0u, 0x64006400u);
+  const uint32_t SUB = 0x64086408u, MUL = 0x2c002c00u, ADD = 0xd480d480u;
+  __half2 a = __hsub2(*reinterpret_cast<const __half2 *>(&l), *reinterpret_cast<const __half2 *>(&SUB));
+  __half2 b = __hfma2(*reinterpret_cast<const __half2 *>(&h), *reinterpret_cast<const __half2 *>(&MUL),
+                      *reinterpret_cast<const __half2 *>(&ADD));
+  a = __hmul2(a, scale);  // group scale in fp16 before the MMA, as the reference does (marlin_cute_trait.h:656-664)
+  b = __hmul2(b, scale);
+  lo = *reinterpret_cast<uint32_t *>(&a);
+  hi = *reinterpret_cast<uint32_t *>(&b);
+}
+
+template <int TM, int KS, bool GROUPED>
+__global__ void __launch_bounds__(Config<TM, KS>::THREADS, 1)
+w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
+                const __grid_constant__ CUtensorMap tmS, const Params p) {
+  using Cfg = Config<TM, KS>;
+  using namespace sm100;
+  constexpr int S = Cfg::STAGES;
+  constexpr int NDQ = Cfg::NDQ;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *sW = smem;                                   // [S][W_BYTES]   1024-aligned each
+  uint8_t *sA = sW + S * Cfg::W_BYTES;                  // [S][A_BYTES]   1024-aligned each
+  uint8_t *sS = sA + S * Cfg::A_BYTES;                  // [S][S_BYTES]
+  Bars *bars = reinterpret_cast<Bars *>(sS + S * Cfg::S_BYTES);
+  volatile int *abort = &bars->abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- this CTA's slice of the linearised (tile, k-step) space
+  const int it_begin = min(p.total_iters, (int)blockIdx.x * p.iters_per_cta);
+  const int it_end = min(p.total_iters, it_begin + p.iters_per_cta);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(smem_u32(&bars->full[i]), 1);
+      mbar_init(smem_u32(&bars->empty[i]), 4 + 1);      // 4 dequant warps + the MMA commit
+    }
+    for (int i = 0; i < Cfg::WBUFS; ++i) {
+      mbar_init(smem_u32(&bars->wfull[i]), 4);
+      mbar_init(smem_u32(&bars->wempty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars->accfull[i]), 1);
+      mbar_init(smem_u32(&bars->accempty[i]), EPI_WARPS);
+    }
+    mbar_init(smem_u32(&bars->drain), 1);
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == NDQ + 5) {  // the MMA warp owns TMEM
+    tmem_alloc(smem_u32(&bars->tmem_base), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == NDQ + 4 && lane == 0) {
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmA);
+    if (GROUPED) tma_prefetch_desc(&tmS);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp < NDQ) {
+    // =========================================================== dequant warps
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may touch
+    const int set = warp >> 2;                 // with 8 warps the two sets alternate k-steps
+    const int row = quad * 32 + lane;          // weight column within the tile = TMEM lane
+    const int nr = row & 63, blk = row >> 6;
+    const int j = nr >> 4, r8 = nr & 7;
+    const uint32_t shift = ((nr >> 3) & 1) ? 8u : 0u;
+    // byte offset of word (r, t) inside a stage, 128-byte-swizzled as TMA wrote it:
+    //   r*1024 + (4*blk + r8/2)*128 + 16*(4*((r8&1)^blk) + (t ^ (r8>>1))) + 4*j
+    const uint32_t base_off = (uint32_t)((4 * blk + (r8 >> 1)) * 128 + 64 * ((r8 & 1) ^ blk) + 4 * j);
+    uint32_t toff[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) toff[t] = base_off + 16u * (uint32_t)(t ^ (r8 >> 1));
+    const uint32_t s_off = (uint32_t)(2 * (64 * blk + 8 * (nr & 7) + (nr >> 3)));  // group-scale slot of this column
+    const uint32_t sW_u = smem_u32(sW), sS_u = smem_u32(sS);
+    const uint32_t one2 = 0x3c003c00u;
+    const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16) + Cfg::WBUF_COL0;
+
+    int step = 0;
+    for (int it = it_begin; it < it_end; ++it, ++step) {
+      if (Cfg::NDQ_SETS == 2 && (step & 1) != set) continue;
+      const int st = step % S, wb = step % Cfg::WBUFS;
+      if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort)) { give_up(p, abort, 1); break; }
+      if (!warp_wait(smem_u32(&bars->wempty[wb]), ((step / Cfg::WBUFS) & 1) ^ 1, abort)) { give_up(p, abort, 2); break; }
+      tc_fence_after();
+      __half2 sc = *reinterpret_cast<const __half2 *>(&one2);
+      if (GROUPED) {
+        uint16_t sv;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sS_u + st * Cfg::S_BYTES + s_off));
+        sc = __half2half2(__ushort_as_half(sv));
+      }
+      const uint32_t wbase = sW_u + st * Cfg::W_BYTES;
+#pragma unroll
+      for (int half = 0; half < KS / 64; ++half) {
+        uint32_t v[32];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            uint32_t w;
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(wbase + (half * 4 + r) * 1024 + toff[t]));
+            dequant_word(w >> shift, sc, v[r * 8 + t], v[r * 8 + 4 + t]);
+          }
+        }
+        tmem_st_32x32b_x32(t_lane + wb * Cfg::WBUF_COLS + half * 32, v);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&bars->wfull[wb]));
+        mbar_arrive(smem_u32(&bars->empty[st]));
+      }
+    }
+  } else if (warp < NDQ + EPI_WARPS) {
+    // =========================================================== epilogue warps
+    // Each warp serves its own TMEM lane quadrant = 32 weight columns, end to end, and publishes its
+    // own flag, so the four warps never have to meet.
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
+    int seg = 0;
+    for (int it = it_begin; it < it_end; ++seg) {
+      const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
+      const int ke = min(p.k_iters, kb + (it_end - it));
+      const int n0 = (tile % p.n_tiles) * TILE_N, m0 = (tile / p.n_tiles) * TM;
+      const int acc = seg & 1;
+      if (!warp_wait(smem_u32(&bars->accfull[acc]), (seg >> 1) & 1, abort)) { give_up(p, abort, 3); break; }
+      tc_fence_after();
+      const bool finisher = (kb == 0);
+      int last_contrib = blockIdx.x;
+      if (finisher && ke < p.k_iters) {
+        // the tile's other k-ranges belong to the next CTAs; they reached this tile first thing
+        last_contrib = ((tile + 1) * p.k_iters - 1) / p.iters_per_cta;
+        bool ok = true;
+        for (int c = blockIdx.x + 1; c <= last_contrib && ok; ++c) {
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t i = 0;
+          while (ld_acquire_gpu(p.flags + 4 * c + quad) != p.epoch) {
+            if ((++i & 0x3f) == 0 && (*abort || globaltimer_ns() - t0 > WAIT_LIMIT_NS)) { ok = false; break; }
+          }
+        }
+        if (!__all_sync(0xffffffffu, ok)) { give_up(p, abort, 4); break; }
+      }
+      __half sch = __float2half(1.0f);
+      if (!GROUPED && finisher) {
+        const int c32 = row & 31;  // per-channel scales are permuted inside 32-column blocks (marlin.py:52-54)
+        sch = p.s[n0 + row - c32 + 8 * ((c32 & 7) >> 1) + 2 * (c32 >> 3) + (c32 & 1)];
+      }
+      float *part = p.partials + ((size_t)blockIdx.x * TM) * TILE_N + row;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TM; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(t_lane + acc * Cfg::ACC_STRIDE + c0, v);
+        tc_wait_ld();
+        if (!finisher) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) part[(size_t)(c0 + i) * TILE_N] = __uint_as_float(v[i]);
+        } else {
+          for (int c = blockIdx.x + 1; c <= last_contrib; ++c) {
+            const float *src = p.partials + ((size_t)c * TM + c0) * TILE_N + row;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(src + (size_t)i * TILE_N));
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int mm = m0 + c0 + i;
+            __half h = __float2half(__uint_as_float(v[i]));
+            if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
+            if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->accempty[acc]));
+      if (!finisher) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(p.flags + 4 * blockIdx.x + quad, p.epoch);
+      }
+      it += ke - kb;
+    }
+  } else if (warp == NDQ + 4) {
+    // =========================================================== TMA producer
+    if (lane == 0) {
+      int step = 0;
+      const uint32_t sW_u = smem_u32(sW), sA_u = smem_u32(sA), sS_u = smem_u32(sS);
+      for (int it = it_begin; it < it_end; ++it, ++step) {
+        const int tile = it / p.k_iters, kk = it - tile * p.k_iters;
+        const int n_idx = tile % p.n_tiles, m0 = (tile / p.n_tiles) * TM;
+        const int st = step % S;
+        if (!mbar_wait(smem_u32(&bars->empty[st]), ((step / S) & 1) ^ 1, abort, WAIT_LIMIT_NS)) { give_up(p, abort, 5); break; }
+        const uint32_t full = smem_u32(&bars->full[st]);
+        mbar_expect_tx(full, Cfg::W_BYTES + Cfg::A_BYTES + (GROUPED ? Cfg::S_BYTES : 0));
+        // weights: 3-D view [k/16][2n/32][32 int32]; box = KS/16 x 8 x 32 words = KS/16 KiB
+        tma_load_3d(sW_u + st * Cfg::W_BYTES, &tmB, 0, n_idx * 8, kk * (KS / 16), full);
+#pragma unroll
+        for (int h = 0; h < KS / 64; ++h)
+          tma_load_2d(sA_u + st * Cfg::A_BYTES + h * TM * 128, &tmA, kk * KS + h * 64, m0, full);
+        if (GROUPED) tma_load_2d(sS_u + st * Cfg::S_BYTES, &tmS, n_idx * TILE_N, (kk * KS) / 128, full);
+      }
+      if (*abort) {
+        // unwinding: let the copies already issued land before the CTA gives its shared memory back
+        volatile int never = 0;
+        const int issued = step < S ? step : S;
+        for (int i = 0; i < issued; ++i) {
+          const int sidx = step - 1 - i;
+          mbar_wait(smem_u32(&bars->full[sidx % S]), (sidx / S) & 1, &never, 200000000ull);
+        }
+      }
+    }
+  } else {
+    // =========================================================== MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16_f32(TILE_N, TM);
+      int step = 0, seg = 0;
+      bool ok = true;
+      const uint32_t sA_u = smem_u32(sA);
+      for (int it = it_begin; it < it_end && ok; ++seg) {
+        const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
+        const int ke = min(p.k_iters, kb + (it_end - it));
+        const int acc = seg & 1;
+        if (!mbar_wait(smem_u32(&bars->accempty[acc]), ((seg >> 1) & 1) ^ 1, abort, WAIT_LIMIT_NS)) { give_up(p, abort, 6); ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + acc * Cfg::ACC_STRIDE;
+        for (int kk = kb; kk < ke; ++kk, ++step) {
+          const int st = step % S, wb = step % Cfg::WBUFS;
+          if (!mbar_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort, WAIT_LIMIT_NS)) { give_up(p, abort, 7); ok = false; break; }
+          if (!mbar_wait(smem_u32(&bars->wfull[wb]), (step / Cfg::WBUFS) & 1, abort, WAIT_LIMIT_NS)) { give_up(p, abort, 8); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_tmem = tmem + Cfg::WBUF_COL0 + wb * Cfg::WBUF_COLS;
+#pragma unroll
+          for (int q = 0; q < KS / 16; ++q) {
+            const uint32_t a_sm = sA_u + st * Cfg::A_BYTES + (q >> 2) * (TM * 128) + (q & 3) * 32;
+            tc_mma_ts(d_tmem, a_tmem + q * 8, make_smem_desc_sw128(a_sm), idesc, (kk > kb || q > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&bars->empty[st]));
+          tc_commit(smem_u32(&bars->wempty[wb]));
+        }
+        if (ok) tc_commit(smem_u32(&bars->accfull[acc]));
+        it += ke - kb;
+      }
+      if (!ok || *abort) {
+        // unwinding: no tcgen05.mma may still be running when TMEM is freed
+        volatile int never = 0;
+        tc_commit(smem_u32(&bars->drain));
+        mbar_wait(smem_u32(&bars->drain), 0, &never, 200000000ull);
+      }
+    }
+  }
+
+  // ---- teardown: everyone meets here, also after an abort (every wait above is bounded)
+  tc_fence_before();
+  __syncthreads();
+  if (warp == NDQ + 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace w4a16

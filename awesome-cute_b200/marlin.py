@@ -1,0 +1,196 @@
+"""Host-side mirror of the reference's Python surface for the W4A16 path
+(gemm/marlin_gemm/marlin.py: ``mul`` :11-24, ``Layer`` :60-131) on top of the C ABI.
+
+Same names, argument meaning and error behaviour; torch is used only to hold device memory and to
+name the current stream.  The arithmetic is in libw4a16.so: the sm_100a kernel for ``mul``, the C++
+packer for ``Layer.pack``.
+"""
+import ctypes
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import _lib
+
+_L = _lib.lib
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _check(err, prob_m, prob_n, prob_k, thread_k, thread_n, groupsize):
+    # the messages of gemm/marlin_gemm/marlin_gemm.cpp:48-55
+    if err == _lib.ERR_PROB_SHAPE:
+        raise RuntimeError("Problem (m=%d, n=%d, k=%d) not compatible with thread_k=%d, thread_n=%d."
+                           % (prob_m, prob_n, prob_k, thread_k, thread_n))
+    if err == _lib.ERR_KERN_SHAPE:
+        raise RuntimeError("No kernel implementation for thread_k=%d, thread_n=%d, groupsize=%d."
+                           % (thread_k, thread_n, groupsize))
+    if err != _lib.OK:
+        raise RuntimeError("w4a16_marlin_gemm failed with code %d: %s" % (err, _lib.last_cuda_error()))
+
+
+def mul(A, B, C, s, workspace, thread_k=-1, thread_n=-1, sms=-1, max_par=16, cute_version=True, _entry=None):
+    """Marlin FP16xINT4 multiply (reference: marlin.py:11-24 -> marlin_gemm.cpp:19-56).
+    @A: `torch.half` input matrix of shape `(m, k)` in standard row-major layout
+    @B: `torch.int` weight matrix of original shape `(k, n)` in Marlin format; see `Layer.pack()`
+    @C: `torch.half` out matrix of shape `(m, n)` in standard row-major layout
+    @s: `torch.half` scales of shape `(k / groupsize, n)`
+    @workspace: `torch.int` tensor with at least `n / 128 * max_par` entries that are all zero
+    @thread_k, @thread_n, @sms, @max_par: as in the reference; -1 = automatic
+    @cute_version: accepted for signature compatibility; there is one kernel here
+    """
+    prob_m, prob_k = A.shape[0], A.shape[1]
+    prob_n = C.shape[1]
+    groupsize = -1 if s.shape[0] == 1 else prob_k // s.shape[0]
+    if groupsize != -1 and groupsize * s.shape[0] != prob_k:
+        raise RuntimeError("k=%d not compatible with %d groups." % (prob_k, s.shape[0]))
+    need = _L.w4a16_workspace_ints(prob_n, max_par)
+    if workspace.numel() < need:
+        raise RuntimeError("workspace must be of size at least %d." % need)
+    if not A.is_cuda:
+        raise RuntimeError("mul() needs CUDA tensors; there is no CPU implementation of this operator.")
+    dev = A.get_device()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    fn = _entry or _L.w4a16_marlin_gemm
+    with torch.cuda.device(dev):
+        err = fn(_ptr(A), _ptr(B), _ptr(C), _ptr(s), prob_m, prob_n, prob_k, _ptr(workspace), groupsize, dev,
+                 ctypes.c_void_p(stream), thread_k, thread_n, sms, max_par)
+    _check(err, prob_m, prob_n, prob_k, thread_k, thread_n, groupsize)
+
+
+def mul_simt(A, B, C, s, workspace, thread_k=-1, thread_n=-1, sms=-1, max_par=16):
+    """Same call through the diagnostic CUDA-core kernel (tests only)."""
+    mul(A, B, C, s, workspace, thread_k, thread_n, sms, max_par, _entry=_L.w4a16_marlin_gemm_simt)
+
+
+def device_status(dev=None):
+    """Synchronise the current stream of `dev`; raise if a kernel gave up a bounded wait."""
+    dev = torch.cuda.current_device() if dev is None else dev
+    err = _L.w4a16_device_status(dev, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if err != _lib.OK:
+        raise RuntimeError("w4a16 device status %d: %s" % (err, _lib.last_cuda_error()))
+
+
+# ----------------------------------------------------------------------------- host packer (numpy in, numpy out)
+def _np(a, dt):
+    a = np.ascontiguousarray(a)
+    if a.dtype != dt:
+        raise TypeError("expected %s, got %s" % (dt, a.dtype))
+    return a
+
+
+def _vp(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def pack_weights(q):
+    """uint8 codes [k, n] -> int32 [k/16, 2n] (marlin.py:119-129)."""
+    q = _np(q, np.uint8)
+    k, n = q.shape
+    B = np.empty((k // 16, 2 * n), np.int32)
+    err = _L.w4a16_pack_weights(_vp(q), k, n, _vp(B))
+    if err:
+        raise ValueError("w4a16_pack_weights: code %d" % err)
+    return B
+
+
+def unpack_weights(B, k, n):
+    B = _np(B, np.int32)
+    q = np.empty((k, n), np.uint8)
+    err = _L.w4a16_unpack_weights(_vp(B), k, n, _vp(q))
+    if err:
+        raise ValueError("w4a16_unpack_weights: code %d" % err)
+    return q
+
+
+def permute_scales(s):
+    """fp16 [groups, n] natural order -> kernel order (marlin.py:111-118)."""
+    s = _np(s, np.float16)
+    out = np.empty_like(s)
+    err = _L.w4a16_permute_scales(_vp(s), s.shape[0], s.shape[1], _vp(out))
+    if err:
+        raise ValueError("w4a16_permute_scales: code %d" % err)
+    return out
+
+
+def unpermute_scales(sp):
+    sp = _np(sp, np.float16)
+    out = np.empty_like(sp)
+    err = _L.w4a16_unpermute_scales(_vp(sp), sp.shape[0], sp.shape[1], _vp(out))
+    if err:
+        raise ValueError("w4a16_unpermute_scales: code %d" % err)
+    return out
+
+
+def quantize_pack(weight_nk, scales, groupsize):
+    """All of Layer.pack on host arrays: weight fp16 [n, k] (nn.Linear layout), scales fp16 [groups, n]."""
+    w = _np(weight_nk, np.float16)
+    s = _np(scales, np.float16)
+    n, k = w.shape
+    groups = 1 if groupsize == -1 else k // groupsize
+    B = np.empty((k // 16, 2 * n), np.int32)
+    sp = np.empty((groups, n), np.float16)
+    err = _L.w4a16_quantize_pack(_vp(w), _vp(s), k, n, groupsize, _vp(B), _vp(sp))
+    if err:
+        raise ValueError("w4a16_quantize_pack: code %d" % err)
+    return B, sp
+
+
+def shard_columns(B, s_packed, rank, world):
+    """Column shard `rank` of `world` of a packed layer (B int32 [k/16, 2n], s_packed fp16 [groups, n])."""
+    B = _np(B, np.int32)
+    sp = _np(s_packed, np.float16)
+    k, n = B.shape[0] * 16, B.shape[1] // 2
+    groups = sp.shape[0]
+    if world < 1 or n % world:
+        raise ValueError("n=%d does not split over %d ranks" % (n, world))
+    Bs = np.empty((k // 16, 2 * n // world), np.int32)
+    ss = np.empty((groups, n // world), np.float16)
+    err = _L.w4a16_shard_columns(_vp(B), _vp(sp), k, n, groups, rank, world, _vp(Bs), _vp(ss))
+    if err:
+        raise ValueError("w4a16_shard_columns: code %d" % err)
+    return Bs, ss
+
+
+class Layer(nn.Module):
+    """4-bit (symmetric grouped) linear layer without bias (reference: marlin.py:60-131)."""
+
+    def __init__(self, infeatures, outfeatures, groupsize=-1, cute_version=True):
+        super().__init__()
+        if groupsize not in [-1, 128]:
+            raise ValueError('Only groupsize -1 and 128 are supported.')
+        if infeatures % 128 != 0 or outfeatures % 256 != 0:
+            raise ValueError('`infeatures` must be divisible by 128 and `outfeatures` by 256.')
+        if groupsize == -1:
+            groupsize = infeatures
+        if infeatures % groupsize != 0:
+            raise ValueError('`infeatures` must be divisible by `groupsize`.')
+        self.k = infeatures
+        self.n = outfeatures
+        self.groupsize = groupsize
+        self.cute_version = cute_version
+        self.register_buffer('B', torch.empty((self.k // 16, self.n * 16 // 8), dtype=torch.int))
+        self.register_buffer('s', torch.empty((self.k // groupsize, self.n), dtype=torch.half))
+        self.register_buffer('workspace', torch.zeros(self.n // 128 * 16, dtype=torch.int), persistent=False)
+
+    def forward(self, A):
+        C = torch.empty(A.shape[:-1] + (self.s.shape[1],), dtype=A.dtype, device=A.device)
+        mul(A.view((-1, A.shape[-1])), self.B, C.view((-1, C.shape[-1])), self.s, self.workspace)
+        return C
+
+    def pack(self, linear, scales):
+        """Pack a fake-quantized linear layer (reference: marlin.py:92-131).
+        @linear: fake-quantized `torch.nn.Linear` layer to convert (must be of type `torch.half`)
+        @scales: corresponding quantization scales of shape `(infeatures, groups)`
+        """
+        if linear.weight.dtype != torch.half:
+            raise ValueError('Only `torch.half` weights are supported.')
+        w = linear.weight.data.detach().cpu().contiguous().numpy()          # [n, k]
+        s = scales.detach().t().cpu().contiguous().numpy()                   # [groups, n]
+        gs = -1 if self.groupsize == self.k else self.groupsize
+        B, sp = quantize_pack(w, s, gs)
+        self.B[:, :] = torch.from_numpy(B).to(self.B.device)
+        self.s[:, :] = torch.from_numpy(sp).to(self.s.device)

@@ -1,0 +1,96 @@
+/*
+ * C ABI of the B200 (sm_100a) W4A16 GEMM library: fp16 activations x Marlin-packed int4 weights
+ * with fp16 group (or per-channel) scales, fp32 accumulation, fp16 output.
+ *
+ * Plain pointers and sizes only; no framework types.  Device pointers are caller-owned.  Every
+ * entry point replaces one interface of the reference project (cited as file:line within the
+ * reference tree).  The C++ twin with the reference's exact launcher signature is declared in
+ * marlin_cute.h.
+ */
+#ifndef W4A16_H_
+#define W4A16_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes.  1 and 2 are the reference's (gemm/marlin_gemm/marlin_cute_kernel.cu:4-5,
+ * gemm/marlin_gemm/marlin_gemm.cpp:16-17); larger values are new failure kinds and never alias them. */
+#define W4A16_OK 0
+#define W4A16_ERR_PROB_SHAPE 1 /* n, k not divisible by the tile / group (marlin_cute_kernel.cu:56-58) */
+#define W4A16_ERR_KERN_SHAPE 2 /* no kernel for (thread_k, thread_n, groupsize) (marlin_cute_kernel.cu:105-107) */
+#define W4A16_ERR_CUDA 3       /* a CUDA runtime / driver call failed (see w4a16_last_cuda_error) */
+#define W4A16_ERR_TIMEOUT 4    /* a bounded device-side wait ran out; reported by w4a16_device_status */
+#define W4A16_ERR_ARG 5        /* null pointer, misaligned pointer or size out of range */
+
+/*
+ * The GEMM.  Replaces  int marlin_cute(...)  gemm/marlin_gemm/marlin_cute_kernel.cu:28-31 (and its
+ * caller-side declaration gemm/marlin_gemm/marlin_gemm.cpp:6-9), argument for argument:
+ *   A          fp16 [m, k] row-major, 16-byte aligned                      (device)
+ *   B          int32 [k/16, 2n]  Marlin-packed 4-bit codes, zero-point 8   (device)
+ *   C          fp16 [m, n] row-major, 16-byte aligned, overwritten         (device)
+ *   s          fp16 [k/groupsize, n] (groupsize 128) or [1, n] (groupsize -1), Marlin-permuted (device)
+ *   workspace  int32, >= w4a16_workspace_ints(n, max_par) entries, all zero on entry; left all zero
+ *   groupsize  128 or -1 (one scale per output column)
+ *   dev        ordinal of the CUDA device the pointers live on; must be the current device
+ *   stream     cudaStream_t passed as void*
+ *   thread_k, thread_n   -1 for automatic, else one of the reference's tile pairs (128,128) / (64,256):
+ *              they keep the reference's divisibility and dispatch meaning (same error codes) although
+ *              the sm_100a kernel picks its own tiling
+ *   sms        CTAs to launch, -1 for one per SM (clamped to the SM count of the device)
+ *   max_par    kept for workspace sizing compatibility
+ * Enqueues on `stream` and returns; 0 at once when m, n or k is 0 (marlin_cute_kernel.cu:59-60).
+ * Scratch beyond the caller's workspace (fp32 partial tiles of the stream-K fix-up) is owned by the
+ * library and cached per (device, stream); its first use on a (device, stream) calls cudaMalloc.
+ */
+int w4a16_marlin_gemm(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n, int prob_k,
+                      void *workspace, int groupsize, int dev, void *stream, int thread_k, int thread_n, int sms,
+                      int max_par);
+
+/* Size rule of the caller's lock array: n / 128 * max_par  (gemm/marlin_gemm/marlin_gemm.cpp:29-31,
+ * gemm/marlin_gemm/marlin.py:85). */
+int w4a16_workspace_ints(int prob_n, int max_par);
+
+/* Synchronises `stream` and returns W4A16_OK, or W4A16_ERR_TIMEOUT when a kernel launched on
+ * (dev, stream) since the last call gave up a bounded wait (its output is then undefined), or
+ * W4A16_ERR_CUDA.  The reference has no counterpart: its fix-up spin is unbounded
+ * (include/barrier.h:85-96). */
+int w4a16_device_status(int dev, void *stream);
+
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char *w4a16_last_cuda_error(void);
+
+/* Diagnostic twin of w4a16_marlin_gemm on plain CUDA cores (one thread per output element, reads the
+ * packed layout through its closed form).  Same arguments and return codes.  Never selected
+ * automatically; used by the tests to cross-check the tensor-core kernel on the device. */
+int w4a16_marlin_gemm_simt(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n,
+                           int prob_k, void *workspace, int groupsize, int dev, void *stream, int thread_k,
+                           int thread_n, int sms, int max_par);
+
+/* ---- host-side weight packer (all pointers are HOST memory) -------------------------------- */
+
+/* codes q (uint8 0..15) [k, n] row-major -> B int32 [k/16, 2n].  Replaces the permute + nibble-pack half
+ * of Layer.pack, gemm/marlin_gemm/marlin.py:119-129.  k % 16 == 0, n % 64 == 0. */
+int w4a16_pack_weights(const uint8_t *q, int k, int n, int32_t *B);
+/* Inverse of w4a16_pack_weights. */
+int w4a16_unpack_weights(const int32_t *B, int k, int n, uint8_t *q);
+/* fp16 scales [groups, n] natural column order -> kernel order.  groups > 1: 64-column blocks
+ * (_scale_perm); groups == 1: 32-column blocks (_scale_perm_single).  marlin.py:49-54,111-118. */
+int w4a16_permute_scales(const uint16_t *s, int groups, int n, uint16_t *s_packed);
+int w4a16_unpermute_scales(const uint16_t *s_packed, int groups, int n, uint16_t *s);
+/* All of Layer.pack (gemm/marlin_gemm/marlin.py:92-131): weight fp16 [n, k] (the nn.Linear layout),
+ * scales fp16 [k/groupsize or 1, n]  ->  round(w/s)+8 clamped to 0..15, packed B and permuted s. */
+int w4a16_quantize_pack(const uint16_t *weight_nk, const uint16_t *scales, int k, int n, int groupsize, int32_t *B,
+                        uint16_t *s_packed);
+/* Column shard `rank` of `world` of a packed layer: B_shard int32 [k/16, 2n/world], s_shard
+ * [groups, n/world].  n/world must be a multiple of 128.  No counterpart in the reference (it is single
+ * GPU); valid because both permutations are local to 64-column blocks. */
+int w4a16_shard_columns(const int32_t *B, const uint16_t *s_packed, int k, int n, int groups, int rank, int world,
+                        int32_t *B_shard, uint16_t *s_shard);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4A16_H_ */

@@ -112,7 +112,7 @@ def np_gemm(A, q, s, groupsize):
 
 # ----------------------------------------------------------------------------- C restatement
 def build(force=False):
-    """Compile liboracle.so (and oracle/_ref when the reference checkout is present)."""
+    """Compile liboracle.so."""
     so = os.path.join(_HERE, "liboracle.so")
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(os.path.join(_HERE, "w4a16_oracle.c")):
         subprocess.run(["make", "-C", _HERE, "-s"], check=True, capture_output=True)

@@ -1,0 +1,187 @@
+"""GPU parity tests: the sm_100a kernel, called through the C ABI, against the CPU oracle.
+
+Shape lists follow the reference's own test file (gemm/marlin_gemm/marlin_test.py:78-167); where that
+file only prints a loss, these assert  max|C - C_ref| <= 1e-2 * max|C_ref|  (fp32 compare, fp32
+accumulation in the oracle) and the reference's relative-mean metric < 0.005 (marlin_test.py:74-75).
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from gpu_common import DEV, check, orc, pack_problem, pkg, run_mul, run_problem, to_dev
+
+
+def test_simt_cross_check():
+    run_problem(16, 512, 1024, groupsize=128, fn=pkg.mul_simt)
+    run_problem(3, 512, 192, 64, 256, groupsize=-1, fn=pkg.mul_simt)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 12, 16, 24, 32, 48, 64, 118, 128, 152, 768, 1024])
+def test_tiles(m):  # marlin_test.py:78-84
+    for thread_k, thread_n in [(64, 256), (128, 128)]:
+        if m > 16 and thread_k == 128:
+            continue
+        run_problem(m, 2 * 256, 1024, thread_k, thread_n, seed=m)
+
+
+@pytest.mark.parametrize("k", [3 * 64 + 64 * 4 * 2 + 64 * i for i in range(1, 4)])
+def test_k_stages_divisibility(k):  # marlin_test.py:86-89
+    run_problem(16, 2 * 256, k, 64, 256, seed=k)
+
+
+@pytest.mark.parametrize("k", [64, 128, 192])
+def test_very_few_stages(k):  # marlin_test.py:91-94
+    run_problem(16, 2 * 256, k, 64, 256, seed=k)
+
+
+def test_errors():  # marlin_test.py:96-121
+    m, n, k = 16, 256, 64
+    A, q, s = orc.make_problem(m, n, k, -1, 0)
+    At, Bt, st = pack_problem(A, q, s)
+    C = torch.zeros((m, n), dtype=torch.half, device=DEV)
+    ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=DEV)
+    with pytest.raises(RuntimeError, match="not compatible with thread_k=128"):
+        pkg.mul(At, Bt, C, st, ws, 128, 128, -1)
+    with pytest.raises(RuntimeError, match="not compatible with thread_k=256"):
+        pkg.mul(At, Bt, C, st, ws, 256, 256, -1)
+    s2 = torch.zeros((2, n), dtype=torch.half, device=DEV)
+    with pytest.raises(RuntimeError):
+        pkg.mul(At, Bt, C, s2, ws, 256, 256, -1)
+    assert float(C.abs().sum()) == 0.0   # nothing was launched
+
+
+@pytest.mark.parametrize("groupsize", [128, -1])
+@pytest.mark.parametrize("n,k", [(256, 512), (256, 1024), (256 * 128, 1024)])
+def test_groups(groupsize, n, k):  # marlin_test.py:123-131
+    run_problem(16, n, k, 128, 128, groupsize, seed=n + k)
+
+
+LLAMA = {  # marlin_test.py:133-167, (k, n) per layer
+    "7B": [(4096, 3 * 4096), (4096, 4096), (4096, 2 * 10752), (10752, 4096)],
+    "13B": [(5120, 3 * 5120), (5120, 5120), (5120, 2 * 13568), (13568, 5120)],
+    "33B": [(6656, 3 * 6656), (6656, 6656), (6656, 2 * 17664), (17664, 6656)],
+    "70B": [(8192, 3 * 8192), (8192, 8192), (8192, 2 * 21760), (21760, 8192)],
+}
+
+
+@pytest.mark.parametrize("model", sorted(LLAMA))
+def test_llama_shapes(model):
+    for k, n in LLAMA[model]:
+        for batch in [1, 16]:
+            run_problem(batch, n, k, 128, 128, -1, seed=batch)
+
+
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 16, 32, 64])
+@pytest.mark.parametrize("n,k", [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)])
+def test_decode_sweep_g128(m, n, k):
+    """The benchmark's decode configs (Llama-2-7B layer shapes, group 128)."""
+    run_problem(m, n, k, groupsize=128, seed=m)
+
+
+@pytest.mark.parametrize("sms", [1, 2, 3, 5, 7, 31, 64, 147, 148])
+def test_stream_k_split_counts(sms):
+    """Every way of cutting tiles between CTAs, including CTAs that hold only a middle slice of one tile."""
+    run_problem(16, 512, 2048, groupsize=128, seed=sms, sms=sms)
+    run_problem(40, 256, 4096, groupsize=-1, seed=sms, sms=sms)
+    run_problem(200, 384, 1024, groupsize=128, seed=sms, sms=sms)
+
+
+@pytest.mark.parametrize("m", [16, 128])
+def test_stream_k_large_k(m):
+    """Skinny-m / large-k config: N=8192, K=28672 (oracle on a column window to stay in seconds)."""
+    n, k, gs = 8192, 28672, 128
+    A, q, s = orc.make_problem(m, n, k, gs, 11)
+    At, Bt, st = pack_problem(A, q, s)
+    C = run_mul(At, Bt, st, m, n)
+    for n0 in (0, 3968, 8192 - 256):
+        ref = orc.c_gemm(A, np.ascontiguousarray(q[:, n0:n0 + 256]), np.ascontiguousarray(s[:, n0:n0 + 256]), gs)
+        check(C[:, n0:n0 + 256], ref, "window %d" % n0)
+
+
+def test_repeated_calls_share_scratch_and_workspace():
+    """One workspace and one stream over many calls (marlin_profiling.py:59-70 does this); different
+    shapes back to back so partial tiles of one call are overwritten by the next."""
+    ws = torch.zeros(4096 // 128 * 16, dtype=torch.int, device=DEV)
+    probs = []
+    for i, (m, n, k, gs) in enumerate([(16, 512, 2048, 128), (64, 1024, 1024, -1), (16, 512, 2048, 128), (130, 256, 512, 128)]):
+        A, q, s = orc.make_problem(m, n, k, gs, 100 + i)
+        probs.append((A, q, s, gs) + pack_problem(A, q, s))
+    outs = []
+    for rep in range(3):
+        for (A, q, s, gs, At, Bt, st) in probs:
+            C = torch.zeros((A.shape[0], q.shape[1]), dtype=torch.half, device=DEV)
+            pkg.mul(At, Bt, C, st, ws)
+            outs.append((C, A, q, s, gs))
+    pkg.device_status(0)
+    assert int(ws.abs().sum().item()) == 0
+    for (C, A, q, s, gs) in outs:
+        check(C, orc.c_gemm(A, q, s, gs))
+
+
+def test_deterministic():
+    A, q, s = orc.make_problem(16, 1024, 4096, 128, 5)
+    At, Bt, st = pack_problem(A, q, s)
+    C1 = run_mul(At, Bt, st, 16, 1024)
+    C2 = run_mul(At, Bt, st, 16, 1024)
+    assert torch.equal(C1, C2)
+
+
+def test_tc_matches_simt_bitwise_close():
+    """Two independent device implementations on the same operands."""
+    A, q, s = orc.make_problem(48, 512, 1024, 128, 9)
+    At, Bt, st = pack_problem(A, q, s)
+    C1 = run_mul(At, Bt, st, 48, 512).float()
+    C2 = run_mul(At, Bt, st, 48, 512, fn=pkg.mul_simt).float()
+    assert float((C1 - C2).abs().max()) <= 2e-3 * float(C2.abs().max())
+
+
+def test_golden_from_reference_packer(golden_dir):
+    """Operands packed by the REFERENCE's Layer.pack (stored fixtures) through the kernel, against the
+    reference's own matmul result stored beside them."""
+    import glob, os
+    for path in sorted(glob.glob(os.path.join(golden_dir, "g*.npz"))):
+        g = np.load(path)
+        m, n, k, gs = int(g["m"]), int(g["n"]), int(g["k"]), int(g["groupsize"])
+        if g["s_packed"].shape[0] == 1:
+            gs = -1
+        tk, tn = (128, 128) if k % 128 == 0 else (64, 256)
+        C = run_mul(to_dev(g["A"]), to_dev(g["B"]), to_dev(g["s_packed"]), m, n, tk, tn)
+        check(C, g["C_ref32"], os.path.basename(path))
+
+
+def test_linearity_at_full_size():
+    """Size-independent property at a benchmark shape: GEMM(a1 + a2) == GEMM(a1) + GEMM(a2) up to fp16
+    rounding of the three outputs."""
+    m, n, k = 16, 22016, 4096
+    A, q, s = orc.make_problem(m, n, k, 128, 21)
+    A2 = np.random.default_rng(22).standard_normal((m, k), dtype=np.float32).astype(np.float16)
+    A1h = (A.astype(np.float32) * 0.5).astype(np.float16)
+    A2h = (A2.astype(np.float32) * 0.5).astype(np.float16)
+    Asum = (A1h.astype(np.float32) + A2h.astype(np.float32)).astype(np.float16)
+    _, Bt, st = pack_problem(A, q, s)
+    C1 = run_mul(to_dev(A1h), Bt, st, m, n).float()
+    C2 = run_mul(to_dev(A2h), Bt, st, m, n).float()
+    Cs = run_mul(to_dev(Asum), Bt, st, m, n).float()
+    # Asum is rounded to fp16 once more than A1h, A2h: allow that rounding through the GEMM
+    assert float((Cs - (C1 + C2)).abs().max()) <= 1e-2 * float(Cs.abs().max())
+
+
+def test_layer_forward_like_reference_module():
+    """marlin.Layer: pack() + forward() (marlin.py:60-131) on the device."""
+    k, n, gs = 512, 512, 128
+    rng = np.random.default_rng(3)
+    A, q, s = orc.make_problem(24, n, k, gs, 3)
+    ref = orc.np_dequant(q, s, gs)                      # fake-quantised fp16 weights [k, n]
+    linear = torch.nn.Linear(k, n, bias=False).half()
+    linear.weight.data = torch.from_numpy(np.ascontiguousarray(ref.T))
+    layer = pkg.Layer(k, n, groupsize=gs)
+    layer.pack(linear, torch.from_numpy(np.ascontiguousarray(s.T)))
+    assert np.array_equal(layer.B.numpy(), pkg.pack_weights(q))
+    layer = layer.to(DEV)
+    out = layer(to_dev(A).view(2, 12, k))
+    pkg.device_status(0)
+    assert tuple(out.shape) == (2, 12, n)
+    check(out.view(24, n), orc.c_gemm(A, q, s, gs))
