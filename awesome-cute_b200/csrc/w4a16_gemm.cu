@@ -63,13 +63,12 @@ bool encode(CUtensorMap *map, CUtensorMapDataType dt, int rank, const void *base
   return true;
 }
 
-// Per (device, stream) state: scratch of the stream-K fix-up, the status word, the launch epoch.
+// Per (device, stream) state: scratch and flags of the stream-K fix-up, the status word.
 struct StreamCtx {
   float *partials = nullptr;
   size_t partial_floats = 0;
-  uint32_t *flags = nullptr;  // [MAX_GRID][4]
+  uint32_t *flags = nullptr;  // [MAX_GRID][4], all zero between launches
   int *status = nullptr;
-  uint32_t epoch = 0;
 };
 constexpr int MAX_GRID = 256;
 
@@ -177,11 +176,9 @@ int launch_tc(const Problem &pr) {
   }
   StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 128 * w4a16::TILE_N);
   if (!ctx) return W4A16_ERR_CUDA;
-  if (++ctx->epoch == 0) ctx->epoch = 1;
   p.partials = ctx->partials;
   p.flags = ctx->flags;
   p.status = ctx->status;
-  p.epoch = ctx->epoch;
   kern<<<grid, Cfg::THREADS, smem, pr.stream>>>(tmB, tmA, tmS, p);
   if (!cuda_ok(cudaGetLastError(), "kernel launch")) return W4A16_ERR_CUDA;
   return W4A16_OK;
@@ -311,16 +308,20 @@ extern "C" int w4a16_device_status(int dev, void *stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return W4A16_ERR_CUDA;
   int *status = nullptr;
+  uint32_t *flags = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_mu);
     auto it = g_ctx.find({dev, st});
     if (it == g_ctx.end()) return W4A16_OK;  // nothing was ever launched here
     status = it->second.status;
+    flags = it->second.flags;
   }
   int word = 0;
   if (!cuda_ok(cudaMemcpy(&word, status, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy(status)")) return W4A16_ERR_CUDA;
   if (word == 0) return W4A16_OK;
   if (!cuda_ok(cudaMemset(status, 0, sizeof(int)), "cudaMemset(status)")) return W4A16_ERR_CUDA;
+  // a kernel that gave up may have left fix-up flags raised
+  if (!cuda_ok(cudaMemset(flags, 0, sizeof(uint32_t) * 4 * MAX_GRID), "cudaMemset(flags)")) return W4A16_ERR_CUDA;
   g_last_error = "device-side wait timed out at site " + std::to_string(word >> 8);
   return W4A16_ERR_TIMEOUT;
 }

@@ -27,7 +27,9 @@
 // Work split: stream-K.  The (tile, k-step) space is linearised tile-major, n fastest
 // (marlin_cute_trait.h:278-286 uses the same order) and cut into equal contiguous ranges, one per CTA.
 // A tile cut between CTAs is finished by the CTA that holds its k-step 0; the others store their fp32
-// partial tile to library-owned scratch and publish a per-CTA flag (release) carrying the launch epoch.
+// partial tile to library-owned scratch and raise a flag (release); the finisher lowers it again after
+// reading, so the flags are all zero between launches (the contract the reference's lock array has,
+// marlin_cute_trait.h:941-945) and a launch can be replayed from a CUDA graph.
 // The finisher reaches that tile LAST in its own range while the contributors reach it FIRST in theirs,
 // so in practice it never waits; contributors never wait at all (no serial chain as in
 // marlin_cute_trait.h:935-950).  The finisher's wait is bounded like every other wait in the kernel.
@@ -48,8 +50,7 @@ struct Params {
   const __half *s;                      // scales (read directly by the epilogue when per-channel)
   __half *C;
   float *partials;                      // [gridDim.x][TM][128] fp32 partial tiles (stream-K fix-up)
-  uint32_t *flags;                      // [gridDim.x][4] epoch flags, one per epilogue warp
-  uint32_t epoch;                       // this launch's number (never 0)
+  uint32_t *flags;                      // [gridDim.x][4], one per epilogue warp; zero between launches
   int *status;                          // 0, or STATUS_TIMEOUT | (site << 8)
 };
 
@@ -253,7 +254,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
         for (int c = blockIdx.x + 1; c <= last_contrib && ok; ++c) {
           const uint64_t t0 = globaltimer_ns();
           uint32_t i = 0;
-          while (ld_acquire_gpu(p.flags + 4 * c + quad) != p.epoch) {
+          while (ld_acquire_gpu(p.flags + 4 * c + quad) == 0u) {
             if ((++i & 0x3f) == 0 && (*abort || globaltimer_ns() - t0 > WAIT_LIMIT_NS)) { ok = false; break; }
           }
         }
@@ -294,7 +295,10 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       if (!finisher) {
         __threadfence();
         __syncwarp();
-        if (lane == 0) st_release_gpu(p.flags + 4 * blockIdx.x + quad, p.epoch);
+        if (lane == 0) st_release_gpu(p.flags + 4 * blockIdx.x + quad, 1u);
+      } else if (lane == 0) {
+        // every lane has read the partial tiles (the __syncwarp above): lower the flags for the next launch
+        for (int c = blockIdx.x + 1; c <= last_contrib; ++c) p.flags[4 * c + quad] = 0u;
       }
       it += ke - kb;
     }

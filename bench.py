@@ -1,0 +1,401 @@
+"""Benchmark of the W4A16 (Marlin-layout) GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1] at its M = 16 point): one STEP is the four Llama-2-7B linear layers
+(N,K) = (12288,4096), (4096,4096), (22016,4096), (4096,11008), group size 128, batch M = 16, fp16
+activations ~N(0,1), int4 codes uniform with zero-point 8, fp16 scales uniform in [0.005, 0.02]:
+four GEMM launches that stream 101 MB of packed weights.  Weights rotate over 3 resident copies
+(303 MB > 126 MB L2) so every launch reads its weights from HBM.
+
+metric / value   weight HBM GB/s = packed-weight bytes of all ranks / time (CUDA events, max over ranks);
+                 the K timed steps are replayed from one CUDA graph so the figure is the kernels', not
+                 Python's launch path
+e2e              the same metric through the public call `mul()` with HOST buffers: per GEMM the
+                 activations are copied from pinned host memory and the output copied back, no graph;
+                 weights stay resident on the device as a layer's parameters do (marlin.py:82-83)
+roofline         HBM bound: algorithmic bytes (weights + scales + A + C) per launch / mean launch time
+cpu_baseline     the CPU oracle (dequantise + fp32 GEMM, all host threads) on one full step
+prefill          extra: TFLOP/s at M = 4096 on the same four shapes (BASELINE.json configs[2])
+N > 1            every rank runs the same per-GPU workload on its own column shard of a layer N times as
+                 wide (weak scaling, no collective on the data path); `gathered` reports the step with
+                 an NCCL all-gather of the fp16 outputs added
+--impl reference the reference has no runnable CPU or sm_100 implementation of this path, so this arm
+                 times the CPU restatement of its algorithm (oracle/, kind "port") on rank 0 only
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SHAPES = [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)]   # (N, K) of Llama-2-7B linears
+GROUP = 128
+M_DECODE = 16
+COPIES = 3
+METRIC = "w4a16_weight_hbm_gbs_m16"
+UNIT = "GB/s"
+WORKLOAD = "llama2-7b linears (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)}, M=16, g128"
+
+
+def weight_bytes(shapes):
+    return sum(n * k // 2 for n, k in shapes)
+
+
+def algorithmic_bytes(m, n, k, g=GROUP):
+    return n * k // 2 + 2 * (k // g) * n + 2 * m * k + 2 * m * n
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        return {"hbm_gbs": float(pk["hbm_gbs"]), "bf16_tflops": float(pk["bf16_tflops"]),
+                "bf16_tflops_sustained": float(pk.get("bf16_tflops_sustained", pk["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------------------------------- clocks
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the measurements run."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop_evt = threading.Event()
+        self.active = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            }
+            while not self._stop_evt.is_set():
+                if self.active.is_set():
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                    try:
+                        mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                    except Exception:
+                        mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    for bit, name in names.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                time.sleep(0.002)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.reasons.add("nvml_unavailable:%s" % type(e).__name__)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+
+    def summary(self):
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------------------- reference arm
+def cpu_time_step(threads_note=True, reps=1):
+    """One full step (four GEMMs, M = 16) through the CPU oracle; returns (seconds, threads)."""
+    from oracle import oracle as orc
+    probs = [orc.make_problem(M_DECODE, n, k, GROUP, seed=i) for i, (n, k) in enumerate(SHAPES)]
+    orc.c_gemm(*probs[1], GROUP)  # warm the thread pool
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for (A, q, s) in probs:
+            orc.c_gemm(A, q, s, GROUP)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best, orc.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    probs = [orc.make_problem(M_DECODE, n, k, GROUP, seed=i) for i, (n, k) in enumerate(SHAPES)]
+    for _ in range(args.warmup):
+        orc.c_gemm(*probs[1], GROUP)
+    steps = min(args.steps, 20)   # bounded: one step is ~0.5 s of CPU work on 8 cores
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for (A, q, s) in probs:
+            orc.c_gemm(A, q, s, GROUP)
+    dt = (time.perf_counter() - t0) / steps
+    val = weight_bytes(SHAPES) / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference algorithm (dequantise + fp32 GEMM); "
+                   "the reference ships no CPU kernel and its CUDA kernels do not run on sm_100"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+                         "sample": "%d full steps (4 GEMMs, M=16, 101 MB of packed weights each)" % steps},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()   # raises if libw4a16.so is missing: there is no fallback
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    peaks = load_peaks()
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+
+    def make_layer(n, k, copies):
+        """Random packed operands straight on the device: any int32 is a valid packed word (eight
+        uniform codes) and the scale permutation of uniform values is uniform."""
+        Bs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen)
+              for _ in range(copies)]
+        ss = [(torch.rand((k // GROUP, n), device=dev, generator=gen) * 0.015 + 0.005).half() for _ in range(copies)]
+        return Bs, ss
+
+    layers = [make_layer(n, k, COPIES) for (n, k) in SHAPES]
+    acts = [torch.randn((M_DECODE, k), device=dev, generator=gen).half() for (_, k) in SHAPES]
+    outs = [torch.zeros((M_DECODE, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
+    wss = [torch.zeros(n // 128 * 16, dtype=torch.int, device=dev) for (n, _) in SHAPES]
+
+    def step(i):
+        c = i % COPIES
+        for li in range(len(SHAPES)):
+            pkg.mul(acts[li], layers[li][0][c], outs[li], layers[li][1][c], wss[li])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    # ---- warm-up (eager, on the stream the graph will be captured on)
+    side = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(side):
+        for i in range(max(args.warmup, 3)):
+            step(i)
+    side.synchronize()
+    pkg.device_status(local)
+
+    # ---- value: K steps captured in one CUDA graph, timed with events on the replay stream
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(args.steps):
+            step(i)
+    graph.replay()               # untimed: first replay uploads the graph
+    barrier()
+    sampler.active.set()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_per_step = ms_total / args.steps
+    launches = args.steps * len(SHAPES)
+    wbytes = weight_bytes(SHAPES)
+    value = world * wbytes / (ms_per_step * 1e-3) / 1e9
+
+    alg = sum(algorithmic_bytes(M_DECODE, n, k) for n, k in SHAPES)
+    achieved = alg / (ms_per_step * 1e-3) / 1e9     # per launch == per step here (same 4 launches / same time)
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "kernel": "w4a16_tc_kernel<16,128,grouped>", "launch_us": ms_total * 1e3 / launches,
+                "algorithmic_bytes_per_launch": alg / len(SHAPES)}
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            with open(traffic_file) as f:
+                roofline["traffic"] = json.load(f).get("dram_bytes_per_launch_m16_step_mean")
+        except Exception:
+            pass
+
+    # ---- e2e: the public call with host buffers, no graph
+    hA = [a.cpu().pin_memory() for a in acts]
+    hC = [torch.empty((M_DECODE, n), dtype=torch.half).pin_memory() for (n, _) in SHAPES]
+
+    def e2e_step(i):
+        c = i % COPIES
+        for li in range(len(SHAPES)):
+            acts[li].copy_(hA[li], non_blocking=True)
+            pkg.mul(acts[li], layers[li][0][c], outs[li], layers[li][1][c], wss[li])
+            hC[li].copy_(outs[li], non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    e2e = {"value": world * wbytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+           "h2d_bytes_per_step": sum(2 * M_DECODE * k for _, k in SHAPES),
+           "d2h_bytes_per_step": sum(2 * M_DECODE * n for n, _ in SHAPES), "ms_per_step": e2e_ms}
+
+    # ---- extras: decode sweep and prefill (not the headline; same kernels, same timing method)
+    extras = {}
+    if not args.no_extras:
+        def time_graph(fn, reps):
+            with torch.cuda.stream(side):
+                fn(0)
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(reps):
+                    fn(i)
+            g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps
+
+        sweep = {}
+        for m in (1, 2, 4, 8, 16, 32, 64):
+            am = [torch.randn((m, k), device=dev, generator=gen).half() for (_, k) in SHAPES]
+            cm = [torch.zeros((m, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
+            per_shape = {}
+            for li, (n, k) in enumerate(SHAPES):
+                def one(i, li=li):
+                    c = i % COPIES
+                    pkg.mul(am[li], layers[li][0][c], cm[li], layers[li][1][c], wss[li])
+                # a single layer's 3 copies may fit in L2: pad the rotation with the other layers' traffic
+                ms = time_graph(one, 30)
+                per_shape["%dx%d" % (n, k)] = {"us": ms * 1e3, "weight_gbs": n * k / 2 / (ms * 1e-3) / 1e9}
+            def allfour(i):
+                c = i % COPIES
+                for li in range(len(SHAPES)):
+                    pkg.mul(am[li], layers[li][0][c], cm[li], layers[li][1][c], wss[li])
+            ms = time_graph(allfour, 20)
+            sweep["m%d" % m] = {"step_us": ms * 1e3, "weight_gbs": wbytes / (ms * 1e-3) / 1e9,
+                                "frac_of_peak": wbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "per_shape_l2_warmish": per_shape}
+        extras["decode_sweep"] = sweep
+
+        prefill = {}
+        for m in (1024, 4096):
+            am = [torch.randn((m, k), device=dev, generator=gen).half() for (_, k) in SHAPES]
+            cm = [torch.zeros((m, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
+            res = {}
+            for li, (n, k) in enumerate(SHAPES):
+                def one(i, li=li):
+                    pkg.mul(am[li], layers[li][0][i % COPIES], cm[li], layers[li][1][i % COPIES], wss[li])
+                ms = time_graph(one, 5)
+                tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+                res["%dx%d" % (n, k)] = {"ms": ms, "tflops": tf, "frac_of_peak": tf / peaks["bf16_tflops"]}
+            tot_flops = sum(2.0 * m * n * k for n, k in SHAPES)
+            tot_ms = sum(v["ms"] for v in res.values())
+            prefill["m%d" % m] = {"tflops": tot_flops / (tot_ms * 1e-3) / 1e12,
+                                  "frac_of_peak": tot_flops / (tot_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "per_shape": res}
+            del am, cm
+        extras["prefill"] = prefill
+        extras["peaks"] = peaks
+
+    gathered = None
+    if world > 1:
+        # the step with the fp16 outputs all-gathered along N (only where a caller asks for the full row)
+        gbufs = [torch.empty((world, M_DECODE, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
+
+        def gstep(i):
+            step(i)
+            for li in range(len(SHAPES)):
+                dist.all_gather_into_tensor(gbufs[li], outs[li])
+        for i in range(3):
+            gstep(i)
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            gstep(i)
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        gms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+        gathered = {"value": world * wbytes / (gms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": gms,
+                    "note": "eager launches + NCCL all_gather_into_tensor of the fp16 outputs per layer"}
+
+    sampler.active.clear()
+    sampler.stop()
+    pkg.device_status(local)
+
+    if rank == 0:
+        cpu_s, cpu_threads = cpu_time_step(reps=2) if world == 1 else (None, None)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "weights rotate over %d resident copies (%.0f MB > 126 MB L2)"
+                       % (COPIES, COPIES * wbytes / 1e6), "launch": "K steps replayed from one CUDA graph",
+                       "parallelism": "column shards, one per GPU, no collective" if world > 1 else "single GPU"},
+            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
+        }
+        if cpu_s is not None:
+            line["cpu_baseline"] = {"value": wbytes / cpu_s / 1e9, "unit": UNIT, "cores": cpu_threads, "kind": "port",
+                                    "sample": "one full step (4 GEMMs, M=16, 101 MB of packed weights), best of 2"}
+        if gathered is not None:
+            line["gathered"] = gathered
+        line.update(extras)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the decode sweep and prefill extras")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -231,14 +231,21 @@ int oracle_dequant(const uint8_t *q, const uint16_t *s, int k, int n, int groups
  * tests can check a column window of a large problem.                           */
 __attribute__((target_clones("avx512f", "avx2", "default")))
 static void gemm_rows(const float *Af, const float *Wf, int m, int k, long ldw, long ncols, float *C, long ldc) {
-  /* Wf: [k][ncols] window, C: [m][ncols] window */
-  for (int i = 0; i < m; i++) {
-    float *c = C + (long)i * ldc;
-    for (long j = 0; j < ncols; j++) c[j] = 0.0f;
+  /* Wf: [k][ncols] window, C: [m][ncols] window.  Row blocks of 16 keep the C block in L1 while the
+   * weight window streams through once per block. */
+  for (int i0 = 0; i0 < m; i0 += 16) {
+    const int i1 = i0 + 16 < m ? i0 + 16 : m;
+    for (int i = i0; i < i1; i++) {
+      float *c = C + (long)i * ldc;
+      for (long j = 0; j < ncols; j++) c[j] = 0.0f;
+    }
     for (int kk = 0; kk < k; kk++) {
-      const float a = Af[(long)i * k + kk];
       const float *w = Wf + (long)kk * ldw;
-      for (long j = 0; j < ncols; j++) c[j] += a * w[j];
+      for (int i = i0; i < i1; i++) {
+        const float a = Af[(long)i * k + kk];
+        float *c = C + (long)i * ldc;
+        for (long j = 0; j < ncols; j++) c[j] += a * w[j];
+      }
     }
   }
 }

@@ -86,7 +86,7 @@ def test_stream_k_split_counts(sms):
     """Every way of cutting tiles between CTAs, including CTAs that hold only a middle slice of one tile."""
     run_problem(16, 512, 2048, groupsize=128, seed=sms, sms=sms)
     run_problem(40, 256, 4096, groupsize=-1, seed=sms, sms=sms)
-    run_problem(200, 384, 1024, groupsize=128, seed=sms, sms=sms)
+    run_problem(200, 512, 1024, groupsize=128, seed=sms, sms=sms)
 
 
 @pytest.mark.parametrize("m", [16, 128])
