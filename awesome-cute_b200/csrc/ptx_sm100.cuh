@@ -14,6 +14,20 @@ namespace sm100 {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// One lane of a converged warp.  The tcgen05.mma / TMA issue loops run warp-uniformly and predicate only
+// the instruction itself with this: operands then stay in uniform registers.  Issued from a divergent
+// `if (lane == 0)` branch instead, each tcgen05.mma costs about 130 clocks to issue on B200, against 17
+// (N = 16) to 128 (N = 256) clocks of tensor-pipe time.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t p;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(p));
+  return p != 0;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

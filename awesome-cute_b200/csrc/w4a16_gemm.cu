@@ -151,17 +151,26 @@ int launch_tc(const Problem &pr) {
     if (!encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, pr.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B"))
       return W4A16_ERR_CUDA;
   }
-  {  // activations: fp16 [m][k]; rows past m read as zero
-    const cuuint64_t dims[2] = {(cuuint64_t)pr.k, (cuuint64_t)pr.m};
-    const cuuint64_t strides[1] = {(cuuint64_t)pr.k * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)TM};
-    if (!encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A"))
-      return W4A16_ERR_CUDA;
+  {  // activations: fp16 [m][k]; rows past m read as zero.  Preferred: the 3-D view [k/64][m][64] so that one
+     // box brings a whole stage as KS/64 swizzle atoms; if the driver refuses that stride order, 2-D boxes.
+    const cuuint64_t dims3[3] = {64, (cuuint64_t)pr.m, (cuuint64_t)(pr.k / 64)};
+    const cuuint64_t strides3[2] = {(cuuint64_t)pr.k * 2, 128};
+    const cuuint32_t box3[3] = {64, (cuuint32_t)TM, (cuuint32_t)Cfg::KCHUNKS};
+    p.a_box3d = 1;
+    if (Cfg::KCHUNKS == 1 ||
+        !encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pr.A, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B, "A3")) {
+      const cuuint64_t dims[2] = {(cuuint64_t)pr.k, (cuuint64_t)pr.m};
+      const cuuint64_t strides[1] = {(cuuint64_t)pr.k * 2};
+      const cuuint32_t box[2] = {64, (cuuint32_t)TM};
+      p.a_box3d = 0;
+      if (!encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A"))
+        return W4A16_ERR_CUDA;
+    }
   }
   if (GROUPED) {  // scales: fp16 [k/128][n]
     const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
     const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, 1};
+    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, (cuuint32_t)Cfg::GROUPS};
     if (!encode(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
       return W4A16_ERR_CUDA;
   } else {
@@ -190,12 +199,12 @@ int launch_tc_g(const Problem &pr) {
 }
 
 int dispatch_tc(const Problem &pr) {
-  // batch tile = UMMA N; deep 128-k stages while the activation tile is small
-  const bool k128 = (pr.k % 128) == 0;
-  if (pr.m <= 16) return k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
-  if (pr.m <= 32) return k128 ? launch_tc_g<32, 128>(pr) : launch_tc_g<32, 64>(pr);
+  // batch tile = UMMA N; the k per stage is as deep as the activation tile allows (fewer, larger TMAs)
+  const bool k256 = (pr.k % 256) == 0, k128 = (pr.k % 128) == 0;
+  if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
+  if (pr.m <= 32) return k256 ? launch_tc_g<32, 256>(pr) : k128 ? launch_tc_g<32, 128>(pr) : launch_tc_g<32, 64>(pr);
   if (pr.m <= 64) return k128 ? launch_tc_g<64, 128>(pr) : launch_tc_g<64, 64>(pr);
-  return launch_tc_g<128, 64>(pr);
+  return k128 ? launch_tc_g<128, 128>(pr) : launch_tc_g<128, 64>(pr);
 }
 
 // ---- diagnostic CUDA-core kernel: one thread per output, closed form of the packed layout
@@ -327,3 +336,11 @@ extern "C" int w4a16_device_status(int dev, void *stream) {
 }
 
 extern "C" const char *w4a16_last_cuda_error(void) { return g_last_error.c_str(); }
+
+#ifdef W4A16_TRACE
+// trace builds only: point the kernels at a [gridDim.x][16] uint64 buffer for phase time stamps
+extern "C" int w4a16_debug_set_trace(void *buf) {
+  unsigned long long *p = static_cast<unsigned long long *>(buf);
+  return cuda_ok(cudaMemcpyToSymbol(w4a16::g_trace, &p, sizeof(p)), "cudaMemcpyToSymbol") ? W4A16_OK : W4A16_ERR_CUDA;
+}
+#endif

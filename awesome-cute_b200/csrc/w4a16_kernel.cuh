@@ -17,10 +17,11 @@
 // natural k order, the order of the activation tile.
 //
 // Warp roles (one CTA per SM, persistent):
-//   warps [0, NDQ)        dequant: smem nibbles -> registers -> TMEM operand ring      (NDQ = 4 or 8)
-//   warps [NDQ, NDQ+4)    epilogue: TMEM accumulator -> fix-up -> fp16 -> C
-//   warp  NDQ+4           TMA producer (one lane)
-//   warp  NDQ+5           tcgen05.mma issuer (one lane); also owns the TMEM allocation
+//   warps [0, 8)          dequant: smem nibbles -> registers -> TMEM operand ring; two sets of four
+//                         warps (one per TMEM lane quadrant) take alternate k-stages
+//   warps [8, 12)         epilogue: TMEM accumulator -> fix-up -> fp16 -> C
+//   warp  12              TMA producer (warp-uniform loop, one elected lane issues)
+//   warp  13              tcgen05.mma issuer (same); also owns the TMEM allocation
 // Hand-offs are mbarriers; the accumulator is double buffered in TMEM so the epilogue of one tile
 // overlaps the main loop of the next.
 //
@@ -43,10 +44,34 @@ constexpr int EPI_WARPS = 4;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
 constexpr int STATUS_TIMEOUT = 4;                   // == W4A16_ERR_TIMEOUT
 
+// Optional phase trace (compile with -DW4A16_TRACE): [cta][16] globaltimer stamps.
+#ifdef W4A16_TRACE
+__device__ unsigned long long *g_trace = nullptr;
+#define W4A16_STAMP(slot)                                                           \
+  do {                                                                              \
+    if (g_trace && lane == 0) g_trace[blockIdx.x * 16 + (slot)] = sm100::globaltimer_ns(); \
+  } while (0)
+// cycle buckets accumulated in registers and written once per role: [4096 + cta*16 + slot]
+#define W4A16_CLK() clock64()
+#define W4A16_BUCKET(slot, val)                                                        \
+  do {                                                                                 \
+    if (g_trace && lane == 0) g_trace[4096 + blockIdx.x * 16 + (slot)] = (unsigned long long)(val); \
+  } while (0)
+#else
+#define W4A16_CLK() 0ll
+#define W4A16_BUCKET(slot, val) \
+  do {                          \
+  } while (0)
+#define W4A16_STAMP(slot) \
+  do {                    \
+  } while (0)
+#endif
+
 struct Params {
   int m, n, k;
   int n_tiles, m_tiles, k_iters;        // k_iters = k / KS
   int total_iters, iters_per_cta;
+  int a_box3d;                          // 1: tmA is the 3-D view (one box per stage), 0: 2-D (one box per 64 k)
   const __half *s;                      // scales (read directly by the epilogue when per-channel)
   __half *C;
   float *partials;                      // [gridDim.x][TM][128] fp32 partial tiles (stream-K fix-up)
@@ -54,29 +79,34 @@ struct Params {
   int *status;                          // 0, or STATUS_TIMEOUT | (site << 8)
 };
 
+// Tile configuration.  TM = batch tile (UMMA N); KS = k per pipeline stage.  The stage is the unit of
+// every hand-off; it is made large (256 k for small TM) because issuing a TMA costs the producer
+// 100+ clocks whatever its size, so bytes per TMA instruction is what bounds the load rate.
 template <int TM, int KS>
 struct Config {
   static_assert(TM == 16 || TM == 32 || TM == 64 || TM == 128, "batch tile");
-  static_assert(KS == 64 || KS == 128, "k per stage");
+  static_assert(KS == 64 || KS == 128 || KS == 256, "k per stage");
+  static constexpr int KCHUNKS = KS / 64;                    // 64-k swizzle atoms per stage
+  static constexpr int GROUPS = KS >= 128 ? KS / 128 : 1;    // group-scale rows per stage
   static constexpr int W_BYTES = KS * TILE_N / 2;            // packed weights per stage
-  static constexpr int A_BYTES = TM * KS * 2;                // activations per stage (KS/64 boxes of TM x 128 B)
-  static constexpr int S_BYTES = TILE_N * 2;                 // one row of group scales
+  static constexpr int A_BYTES = TM * KS * 2;                // activations per stage: [KCHUNKS][TM][128 B]
+  static constexpr int S_BYTES = GROUPS * TILE_N * 2;        // group scales per stage
   static constexpr int STAGE_BYTES = W_BYTES + A_BYTES + S_BYTES;
-  static constexpr int WBUFS = 4;                            // TMEM operand ring depth
-  static constexpr int WBUF_COLS = KS / 2;                   // fp16 pairs per lane per stage
   static constexpr int ACC_STRIDE = TM < 32 ? 32 : TM;       // TMEM columns between the two accumulators
   static constexpr int WBUF_COL0 = 2 * ACC_STRIDE;
+  static constexpr int WBUF_COLS = KS / 2;                   // fp16 pairs per lane per stage
   static constexpr int TMEM_COLS = 512;
-  static_assert(WBUF_COL0 + WBUFS * WBUF_COLS <= TMEM_COLS, "TMEM budget");
-  static constexpr int SMEM_BUDGET = 200 * 1024;
-  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int WBUFS_RAW = (TMEM_COLS - WBUF_COL0) / WBUF_COLS;
+  static constexpr int WBUFS = WBUFS_RAW > 4 ? 4 : WBUFS_RAW;  // TMEM operand ring depth
+  static_assert(WBUFS >= 2, "TMEM budget");
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int SMEM_MAX = 227 * 1024;
+  static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static_assert(STAGES >= 3, "ring too shallow");
-  static constexpr int NDQ = TM <= 32 ? 8 : 4;               // dequant warps
-  static constexpr int NDQ_SETS = NDQ / 4;
+  static constexpr int NDQ = 8;                              // dequant warps: two sets of four
   static constexpr int THREADS = (NDQ + EPI_WARPS + 2) * 32;
-  static constexpr int BAR_BYTES = 1024;
-  static constexpr int SMEM_BYTES = STAGES * (W_BYTES + A_BYTES) + STAGES * S_BYTES + BAR_BYTES + 1024 /*align slack*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024 /*align slack*/;
 };
 
 struct Bars {  // lives in shared memory
@@ -93,7 +123,7 @@ struct Bars {  // lives in shared memory
 static_assert(sizeof(Bars) <= 1024, "barrier block");
 
 // A wait whose verdict is the same in every lane of the warp (the tcgen05 ld/st that follow are
-// warp-collective), recording the site on failure.
+// warp-collective).
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *abort) {
   const bool ok = sm100::mbar_wait(bar, parity, abort, WAIT_LIMIT_NS);
   return __all_sync(0xffffffffu, ok);
@@ -107,6 +137,7 @@ __device__ __forceinline__ void give_up(const Params &p, volatile int *abort, in
 // int4 -> fp16 exactly (zero point 8), two weights per instruction, as in the reference's dequant
 // (marlin_cute_trait.h:8-39): OR the nibble into the mantissa of 1024.0 and subtract 1032; the high
 // nibbles carry a factor 16 folded into one fma.
+template <bool SCALE>
 __device__ __forceinline__ void dequant_word(uint32_t w, __half2 scale, uint32_t &lo, uint32_t &hi) {
   const uint32_t l = sm100::lop3_and_or(w, 0x000f000fu, 0x64006400u);
   const uint32_t h = sm100::lop3_and_or(w, 0x00f000f0u, 0x64006400u);
@@ -114,8 +145,10 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 scale, uint32_t
   __half2 a = __hsub2(*reinterpret_cast<const __half2 *>(&l), *reinterpret_cast<const __half2 *>(&SUB));
   __half2 b = __hfma2(*reinterpret_cast<const __half2 *>(&h), *reinterpret_cast<const __half2 *>(&MUL),
                       *reinterpret_cast<const __half2 *>(&ADD));
-  a = __hmul2(a, scale);  // group scale in fp16 before the MMA, as the reference does (marlin_cute_trait.h:656-664)
-  b = __hmul2(b, scale);
+  if (SCALE) {  // group scale in fp16 before the MMA, as the reference does (marlin_cute_trait.h:656-664)
+    a = __hmul2(a, scale);
+    b = __hmul2(b, scale);
+  }
   lo = *reinterpret_cast<uint32_t *>(&a);
   hi = *reinterpret_cast<uint32_t *>(&b);
 }
@@ -128,6 +161,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
   using namespace sm100;
   constexpr int S = Cfg::STAGES;
   constexpr int NDQ = Cfg::NDQ;
+  constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;
+  constexpr uint32_t STAGE_TX = Cfg::W_BYTES + Cfg::A_BYTES + (GROUPED ? Cfg::S_BYTES : 0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -139,46 +174,82 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (warp == 0) W4A16_STAMP(0);   // kernel entry
 
   // ---- this CTA's slice of the linearised (tile, k-step) space
   const int it_begin = min(p.total_iters, (int)blockIdx.x * p.iters_per_cta);
   const int it_end = min(p.total_iters, it_begin + p.iters_per_cta);
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) {
-      mbar_init(smem_u32(&bars->full[i]), 1);
-      mbar_init(smem_u32(&bars->empty[i]), 4 + 1);      // 4 dequant warps + the MMA commit
+  // One stage of loads.  Coordinates: weights are the 3-D view [k/16][2n/32][32 int32] (box KS/16 x 8 x 32
+  // words); activations [k/64][m][64] (box KS/64 x TM x 64) or, as 2-D, one 64 x TM box per 64 k; scales
+  // [k/128][n] (box GROUPS x 128).
+  auto issue_stage = [&](int st, int n_idx, int m0, int kk) {
+    const uint32_t full = smem_u32(&bars->full[st]);
+    mbar_expect_tx(full, STAGE_TX);
+    tma_load_3d(smem_u32(sW) + st * Cfg::W_BYTES, &tmB, 0, n_idx * 8, kk * (KS / 16), full);
+    if (p.a_box3d) {
+      tma_load_3d(smem_u32(sA) + st * Cfg::A_BYTES, &tmA, 0, m0, kk * Cfg::KCHUNKS, full);
+    } else {
+#pragma unroll
+      for (int h = 0; h < Cfg::KCHUNKS; ++h)
+        tma_load_2d(smem_u32(sA) + st * Cfg::A_BYTES + h * TM * 128, &tmA, kk * KS + h * 64, m0, full);
     }
-    for (int i = 0; i < Cfg::WBUFS; ++i) {
-      mbar_init(smem_u32(&bars->wfull[i]), 4);
-      mbar_init(smem_u32(&bars->wempty[i]), 1);
+    if (GROUPED) tma_load_2d(smem_u32(sS) + st * Cfg::S_BYTES, &tmS, n_idx * TILE_N, (kk * KS) / 128, full);
+  };
+
+  // ---- prologue.  The producer warp initialises the barriers and puts the first ring-full of loads in
+  // flight BEFORE the CTA-wide sync, so HBM latency overlaps the TMEM allocation and the sync itself.
+  int pro_step = 0, pro_tile = 0, pro_kk = 0, pro_nidx = 0, pro_m0 = 0;
+  if (warp == PRODUCER_WARP) {
+    if (lane == 0) {
+      for (int i = 0; i < S; ++i) {
+        mbar_init(smem_u32(&bars->full[i]), 1);
+        mbar_init(smem_u32(&bars->empty[i]), 4 + 1);      // 4 dequant warps + the MMA commit
+      }
+      for (int i = 0; i < Cfg::WBUFS; ++i) {
+        mbar_init(smem_u32(&bars->wfull[i]), 4);
+        mbar_init(smem_u32(&bars->wempty[i]), 1);
+      }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(smem_u32(&bars->accfull[i]), 1);
+        mbar_init(smem_u32(&bars->accempty[i]), EPI_WARPS);
+      }
+      mbar_init(smem_u32(&bars->drain), 1);
+      bars->abort = 0;
+      mbar_fence_init();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&bars->accfull[i]), 1);
-      mbar_init(smem_u32(&bars->accempty[i]), EPI_WARPS);
+    __syncwarp();
+    pro_tile = it_begin / p.k_iters;
+    pro_kk = it_begin - pro_tile * p.k_iters;
+    pro_nidx = pro_tile % p.n_tiles;
+    pro_m0 = (pro_tile / p.n_tiles) * TM;
+    const int first = min(S, it_end - it_begin);
+    for (; pro_step < first; ++pro_step) {
+      if (elect_one()) issue_stage(pro_step, pro_nidx, pro_m0, pro_kk);
+      __syncwarp();
+      if (++pro_kk == p.k_iters) {
+        pro_kk = 0;
+        ++pro_tile;
+        if (++pro_nidx == p.n_tiles) { pro_nidx = 0; pro_m0 += TM; }
+      }
     }
-    mbar_init(smem_u32(&bars->drain), 1);
-    bars->abort = 0;
-    mbar_fence_init();
+    W4A16_STAMP(9);                // first ring-full issued
   }
-  if (warp == NDQ + 5) {  // the MMA warp owns TMEM
+  if (warp == MMA_WARP) {          // the MMA warp owns TMEM
     tmem_alloc(smem_u32(&bars->tmem_base), Cfg::TMEM_COLS);
     tmem_relinquish();
-  }
-  if (warp == NDQ + 4 && lane == 0) {
-    tma_prefetch_desc(&tmB);
-    tma_prefetch_desc(&tmA);
-    if (GROUPED) tma_prefetch_desc(&tmS);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = bars->tmem_base;
+  if (warp == 0) W4A16_STAMP(1);   // prologue done
+  const uint32_t tmem = __shfl_sync(0xffffffffu, bars->tmem_base, 0);  // provably warp-uniform
 
   if (warp < NDQ) {
     // =========================================================== dequant warps
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may touch
-    const int set = warp >> 2;                 // with 8 warps the two sets alternate k-steps
+    const int set = warp >> 2;                 // the two sets alternate k-stages
     const int row = quad * 32 + lane;          // weight column within the tile = TMEM lane
     const int nr = row & 63, blk = row >> 6;
     const int j = nr >> 4, r8 = nr & 7;
@@ -194,22 +265,28 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     const uint32_t one2 = 0x3c003c00u;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16) + Cfg::WBUF_COL0;
 
-    int step = 0;
-    for (int it = it_begin; it < it_end; ++it, ++step) {
-      if (Cfg::NDQ_SETS == 2 && (step & 1) != set) continue;
+    long long d_full = 0, d_wempty = 0, d_work = 0;
+    const int nsteps = it_end - it_begin;
+    for (int step = set; step < nsteps; step += 2) {
       const int st = step % S, wb = step % Cfg::WBUFS;
+      const long long c0 = W4A16_CLK();
       if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort)) { give_up(p, abort, 1); break; }
+      const long long c1 = W4A16_CLK();
+      if (warp == 0 && step == 0) W4A16_STAMP(2);   // first stage landed
       if (!warp_wait(smem_u32(&bars->wempty[wb]), ((step / Cfg::WBUFS) & 1) ^ 1, abort)) { give_up(p, abort, 2); break; }
       tc_fence_after();
-      __half2 sc = *reinterpret_cast<const __half2 *>(&one2);
-      if (GROUPED) {
-        uint16_t sv;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sS_u + st * Cfg::S_BYTES + s_off));
-        sc = __half2half2(__ushort_as_half(sv));
-      }
+      const long long c2 = W4A16_CLK();
+      d_full += c1 - c0;
+      d_wempty += c2 - c1;
       const uint32_t wbase = sW_u + st * Cfg::W_BYTES;
 #pragma unroll
-      for (int half = 0; half < KS / 64; ++half) {
+      for (int half = 0; half < Cfg::KCHUNKS; ++half) {
+        __half2 sc = *reinterpret_cast<const __half2 *>(&one2);
+        if (GROUPED) {
+          uint16_t sv;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sS_u + st * Cfg::S_BYTES + (half >> 1) * (TILE_N * 2) + s_off));
+          sc = __half2half2(__ushort_as_half(sv));
+        }
         uint32_t v[32];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
@@ -217,7 +294,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
           for (int t = 0; t < 4; ++t) {
             uint32_t w;
             asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(wbase + (half * 4 + r) * 1024 + toff[t]));
-            dequant_word(w >> shift, sc, v[r * 8 + t], v[r * 8 + 4 + t]);
+            dequant_word<GROUPED>(w >> shift, sc, v[r * 8 + t], v[r * 8 + 4 + t]);
           }
         }
         tmem_st_32x32b_x32(t_lane + wb * Cfg::WBUF_COLS + half * 32, v);
@@ -229,6 +306,12 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
         mbar_arrive(smem_u32(&bars->wfull[wb]));
         mbar_arrive(smem_u32(&bars->empty[st]));
       }
+      d_work += W4A16_CLK() - c2;
+      if (warp == 0 && step == 0) W4A16_STAMP(3);   // first operand tile in TMEM
+    }
+    if (warp == 0) {
+      W4A16_STAMP(4);                               // last dequant of set 0
+      W4A16_BUCKET(4, d_full); W4A16_BUCKET(5, d_wempty); W4A16_BUCKET(6, d_work);
     }
   } else if (warp < NDQ + EPI_WARPS) {
     // =========================================================== epilogue warps
@@ -243,27 +326,31 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       const int ke = min(p.k_iters, kb + (it_end - it));
       const int n0 = (tile % p.n_tiles) * TILE_N, m0 = (tile / p.n_tiles) * TM;
       const int acc = seg & 1;
+      const bool finisher = (kb == 0);
+      // the tile's other k-ranges belong to the next CTAs; they reached this tile first thing
+      const int last_contrib = (finisher && ke < p.k_iters) ? ((tile + 1) * p.k_iters - 1) / p.iters_per_cta : (int)blockIdx.x;
+      const int ncontrib = last_contrib - (int)blockIdx.x;
+      __half sch = __float2half(1.0f);
+      if (!GROUPED && finisher) {
+        const int c32 = row & 31;  // per-channel scales are permuted inside 32-column blocks (marlin.py:52-54)
+        sch = p.s[n0 + row - c32 + 8 * ((c32 & 7) >> 1) + 2 * (c32 >> 3) + (c32 & 1)];
+      }
       if (!warp_wait(smem_u32(&bars->accfull[acc]), (seg >> 1) & 1, abort)) { give_up(p, abort, 3); break; }
       tc_fence_after();
-      const bool finisher = (kb == 0);
-      int last_contrib = blockIdx.x;
-      if (finisher && ke < p.k_iters) {
-        // the tile's other k-ranges belong to the next CTAs; they reached this tile first thing
-        last_contrib = ((tile + 1) * p.k_iters - 1) / p.iters_per_cta;
+      if (warp == NDQ) { if (seg == 0) W4A16_STAMP(5); W4A16_STAMP(6); }   // first / last accumulator ready
+      if (ncontrib > 0) {
+        // lane i polls contributor i (+32, ...): all flags are in flight at once
         bool ok = true;
-        for (int c = blockIdx.x + 1; c <= last_contrib && ok; ++c) {
-          const uint64_t t0 = globaltimer_ns();
+        const uint64_t t0 = globaltimer_ns();
+        for (int c = (int)blockIdx.x + 1 + lane; c <= last_contrib && ok; c += 32) {
           uint32_t i = 0;
           while (ld_acquire_gpu(p.flags + 4 * c + quad) == 0u) {
             if ((++i & 0x3f) == 0 && (*abort || globaltimer_ns() - t0 > WAIT_LIMIT_NS)) { ok = false; break; }
           }
         }
         if (!__all_sync(0xffffffffu, ok)) { give_up(p, abort, 4); break; }
-      }
-      __half sch = __float2half(1.0f);
-      if (!GROUPED && finisher) {
-        const int c32 = row & 31;  // per-channel scales are permuted inside 32-column blocks (marlin.py:52-54)
-        sch = p.s[n0 + row - c32 + 8 * ((c32 & 7) >> 1) + 2 * (c32 >> 3) + (c32 & 1)];
+        __threadfence();   // the other lanes read what the polling lane's acquire made visible
+        if (warp == NDQ) W4A16_STAMP(7);   // contributors' flags seen
       }
       float *part = p.partials + ((size_t)blockIdx.x * TM) * TILE_N + row;
 #pragma unroll 1
@@ -275,10 +362,22 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 16; ++i) part[(size_t)(c0 + i) * TILE_N] = __uint_as_float(v[i]);
         } else {
-          for (int c = blockIdx.x + 1; c <= last_contrib; ++c) {
-            const float *src = p.partials + ((size_t)c * TM + c0) * TILE_N + row;
+          // fixed summation order (ascending contributor) keeps the result deterministic; two
+          // contributors' loads are put in flight together
+          int c = (int)blockIdx.x + 1;
+          for (; c + 1 <= last_contrib; c += 2) {
+            const float *s0 = p.partials + ((size_t)c * TM + c0) * TILE_N + row;
+            const float *s1 = s0 + (size_t)TM * TILE_N;
+            float x0[16], x1[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(src + (size_t)i * TILE_N));
+            for (int i = 0; i < 16; ++i) { x0[i] = __ldcg(s0 + (size_t)i * TILE_N); x1[i] = __ldcg(s1 + (size_t)i * TILE_N); }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint((__uint_as_float(v[i]) + x0[i]) + x1[i]);
+          }
+          if (c <= last_contrib) {
+            const float *s0 = p.partials + ((size_t)c * TM + c0) * TILE_N + row;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(s0 + (size_t)i * TILE_N));
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -301,82 +400,102 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
         for (int c = blockIdx.x + 1; c <= last_contrib; ++c) p.flags[4 * c + quad] = 0u;
       }
       it += ke - kb;
+      if (warp == NDQ) W4A16_STAMP(8);     // (last value wins) epilogue of the last segment done
     }
-  } else if (warp == NDQ + 4) {
-    // =========================================================== TMA producer
-    if (lane == 0) {
-      int step = 0;
-      const uint32_t sW_u = smem_u32(sW), sA_u = smem_u32(sA), sS_u = smem_u32(sS);
-      for (int it = it_begin; it < it_end; ++it, ++step) {
-        const int tile = it / p.k_iters, kk = it - tile * p.k_iters;
-        const int n_idx = tile % p.n_tiles, m0 = (tile / p.n_tiles) * TM;
-        const int st = step % S;
-        if (!mbar_wait(smem_u32(&bars->empty[st]), ((step / S) & 1) ^ 1, abort, WAIT_LIMIT_NS)) { give_up(p, abort, 5); break; }
-        const uint32_t full = smem_u32(&bars->full[st]);
-        mbar_expect_tx(full, Cfg::W_BYTES + Cfg::A_BYTES + (GROUPED ? Cfg::S_BYTES : 0));
-        // weights: 3-D view [k/16][2n/32][32 int32]; box = KS/16 x 8 x 32 words = KS/16 KiB
-        tma_load_3d(sW_u + st * Cfg::W_BYTES, &tmB, 0, n_idx * 8, kk * (KS / 16), full);
-#pragma unroll
-        for (int h = 0; h < KS / 64; ++h)
-          tma_load_2d(sA_u + st * Cfg::A_BYTES + h * TM * 128, &tmA, kk * KS + h * 64, m0, full);
-        if (GROUPED) tma_load_2d(sS_u + st * Cfg::S_BYTES, &tmS, n_idx * TILE_N, (kk * KS) / 128, full);
+  } else if (warp == PRODUCER_WARP) {
+    // =========================================================== TMA producer (rest of the ring)
+    // The whole warp runs the loop (warp-uniform operands); one elected lane issues.
+    long long c_wait = 0, c_issue = 0;
+    const int nsteps = it_end - it_begin;
+    for (; pro_step < nsteps; ++pro_step) {
+      const int st = pro_step % S;
+      const long long c0 = W4A16_CLK();
+      if (!warp_wait(smem_u32(&bars->empty[st]), ((pro_step / S) & 1) ^ 1, abort)) { give_up(p, abort, 5); break; }
+      const long long c1 = W4A16_CLK();
+      c_wait += c1 - c0;
+      if (elect_one()) issue_stage(st, pro_nidx, pro_m0, pro_kk);
+      __syncwarp();
+      if (++pro_kk == p.k_iters) {
+        pro_kk = 0;
+        if (++pro_nidx == p.n_tiles) { pro_nidx = 0; pro_m0 += TM; }
       }
-      if (*abort) {
-        // unwinding: let the copies already issued land before the CTA gives its shared memory back
-        volatile int never = 0;
-        const int issued = step < S ? step : S;
-        for (int i = 0; i < issued; ++i) {
-          const int sidx = step - 1 - i;
-          mbar_wait(smem_u32(&bars->full[sidx % S]), (sidx / S) & 1, &never, 200000000ull);
-        }
+      c_issue += W4A16_CLK() - c1;
+    }
+    W4A16_STAMP(10);                       // last TMA issued
+    W4A16_BUCKET(0, c_wait); W4A16_BUCKET(1, c_issue); W4A16_BUCKET(3, nsteps);
+    if (*abort) {
+      // unwinding: let the copies already issued land before the CTA gives its shared memory back
+      volatile int never = 0;
+      const int issued = pro_step < S ? pro_step : S;
+      for (int i = 0; i < issued; ++i) {
+        const int sidx = pro_step - 1 - i;
+        mbar_wait(smem_u32(&bars->full[sidx % S]), (sidx / S) & 1, &never, 200000000ull);
       }
     }
   } else {
     // =========================================================== MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16_f32(TILE_N, TM);
-      int step = 0, seg = 0;
-      bool ok = true;
-      const uint32_t sA_u = smem_u32(sA);
-      for (int it = it_begin; it < it_end && ok; ++seg) {
-        const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
-        const int ke = min(p.k_iters, kb + (it_end - it));
-        const int acc = seg & 1;
-        if (!mbar_wait(smem_u32(&bars->accempty[acc]), ((seg >> 1) & 1) ^ 1, abort, WAIT_LIMIT_NS)) { give_up(p, abort, 6); ok = false; break; }
+    // The whole warp runs the loop (warp-uniform descriptors); one elected lane issues.
+    constexpr uint32_t idesc = make_idesc_f16_f32(TILE_N, TM);
+    int step = 0, seg = 0;
+    bool ok = true;
+    long long m_full = 0, m_wfull = 0, m_issue = 0, m_acc = 0;
+    const uint32_t sA_u = smem_u32(sA);
+    for (int it = it_begin; it < it_end && ok; ++seg) {
+      const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
+      const int ke = min(p.k_iters, kb + (it_end - it));
+      const int acc = seg & 1;
+      const long long ca = W4A16_CLK();
+      if (!warp_wait(smem_u32(&bars->accempty[acc]), ((seg >> 1) & 1) ^ 1, abort)) { give_up(p, abort, 6); ok = false; break; }
+      m_acc += W4A16_CLK() - ca;
+      const uint32_t d_tmem = tmem + acc * Cfg::ACC_STRIDE;
+      for (int kk = kb; kk < ke; ++kk, ++step) {
+        const int st = step % S, wb = step % Cfg::WBUFS;
+        const long long c0 = W4A16_CLK();
+        if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort)) { give_up(p, abort, 7); ok = false; break; }
+        const long long c1 = W4A16_CLK();
+        if (!warp_wait(smem_u32(&bars->wfull[wb]), (step / Cfg::WBUFS) & 1, abort)) { give_up(p, abort, 8); ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem + acc * Cfg::ACC_STRIDE;
-        for (int kk = kb; kk < ke; ++kk, ++step) {
-          const int st = step % S, wb = step % Cfg::WBUFS;
-          if (!mbar_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort, WAIT_LIMIT_NS)) { give_up(p, abort, 7); ok = false; break; }
-          if (!mbar_wait(smem_u32(&bars->wfull[wb]), (step / Cfg::WBUFS) & 1, abort, WAIT_LIMIT_NS)) { give_up(p, abort, 8); ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_tmem = tmem + Cfg::WBUF_COL0 + wb * Cfg::WBUF_COLS;
+        const long long c2 = W4A16_CLK();
+        m_full += c1 - c0;
+        m_wfull += c2 - c1;
+        const uint32_t a_tmem = tmem + Cfg::WBUF_COL0 + wb * Cfg::WBUF_COLS;
+        const uint64_t b_desc = make_smem_desc_sw128(sA_u + st * Cfg::A_BYTES);
+        if (elect_one()) {
 #pragma unroll
           for (int q = 0; q < KS / 16; ++q) {
-            const uint32_t a_sm = sA_u + st * Cfg::A_BYTES + (q >> 2) * (TM * 128) + (q & 3) * 32;
-            tc_mma_ts(d_tmem, a_tmem + q * 8, make_smem_desc_sw128(a_sm), idesc, (kk > kb || q > 0) ? 1u : 0u);
+            // next 64-k chunk is TM*128 bytes on; 16 k inside a 128-byte swizzle row are 32 bytes on
+            const uint64_t bd = b_desc + (uint64_t)(((q >> 2) * (TM * 128) + (q & 3) * 32) >> 4);
+            tc_mma_ts(d_tmem, a_tmem + q * 8, bd, idesc, (kk > kb || q > 0) ? 1u : 0u);
           }
           tc_commit(smem_u32(&bars->empty[st]));
           tc_commit(smem_u32(&bars->wempty[wb]));
         }
-        if (ok) tc_commit(smem_u32(&bars->accfull[acc]));
-        it += ke - kb;
+        __syncwarp();
+        m_issue += W4A16_CLK() - c2;
+        if (step == 0) W4A16_STAMP(11);    // first MMA issued
       }
-      if (!ok || *abort) {
-        // unwinding: no tcgen05.mma may still be running when TMEM is freed
-        volatile int never = 0;
-        tc_commit(smem_u32(&bars->drain));
-        mbar_wait(smem_u32(&bars->drain), 0, &never, 200000000ull);
-      }
+      if (ok && elect_one()) tc_commit(smem_u32(&bars->accfull[acc]));
+      __syncwarp();
+      it += ke - kb;
+    }
+    W4A16_STAMP(12);                       // last MMA issued
+    W4A16_BUCKET(8, m_full); W4A16_BUCKET(9, m_wfull); W4A16_BUCKET(10, m_issue); W4A16_BUCKET(11, m_acc);
+    if (!ok || *abort) {
+      // unwinding: no tcgen05.mma may still be running when TMEM is freed
+      volatile int never = 0;
+      if (elect_one()) tc_commit(smem_u32(&bars->drain));
+      __syncwarp();
+      mbar_wait(smem_u32(&bars->drain), 0, &never, 200000000ull);
     }
   }
 
   // ---- teardown: everyone meets here, also after an abort (every wait above is bounded)
   tc_fence_before();
   __syncthreads();
-  if (warp == NDQ + 5) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);
+    W4A16_STAMP(13);                       // TMEM freed
   }
 }
 

@@ -383,6 +383,41 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """One shape, eager launches, per-launch device time: the command profilers are pointed at.
+    --case NxKxM[xG]  e.g. 22016x4096x16  (G = 128 default, -1 per-channel)."""
+    import torch
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    parts = [int(x) for x in args.case.split("x")]
+    n, k, m = parts[:3]
+    g = parts[3] if len(parts) > 3 else GROUP
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    copies = max(2, min(8, int(300e6 // (n * k // 2)) + 1))     # rotate through > 2 x L2 of weights
+    Bs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen) for _ in range(copies)]
+    groups = 1 if g == -1 else k // g
+    ss = [(torch.rand((groups, n), device=dev, generator=gen) * 0.015 + 0.005).half() for _ in range(copies)]
+    A = torch.randn((m, k), device=dev, generator=gen).half()
+    C = torch.zeros((m, n), dtype=torch.half, device=dev)
+    ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=dev)
+    for i in range(args.warmup):
+        pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for i, (a, b) in enumerate(evs):
+        a.record()
+        pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
+        b.record()
+    torch.cuda.synchronize()
+    pkg.device_status(0)
+    us = sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
+    med = us[len(us) // 2]
+    print(json.dumps({"case": args.case, "copies": copies, "launch_us_median": med, "launch_us_min": us[0],
+                      "weight_gbs": n * k / 2 / (med * 1e-6) / 1e9, "tflops": 2.0 * m * n * k / (med * 1e-6) / 1e12}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -390,8 +425,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the decode sweep and prefill extras")
+    ap.add_argument("--case", default=None, help="NxKxM[xG]: time one shape with eager launches (profiling aid)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
