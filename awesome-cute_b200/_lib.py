@@ -8,7 +8,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libw4a16.so")
+LIB_PATH = os.environ.get("W4A16_LIB") or os.path.join(_HERE, "libw4a16.so")   # W4A16_LIB: debugging override
 
 OK, ERR_PROB_SHAPE, ERR_KERN_SHAPE, ERR_CUDA, ERR_TIMEOUT, ERR_ARG = 0, 1, 2, 3, 4, 5
 

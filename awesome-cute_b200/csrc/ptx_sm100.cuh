@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a features the W4A16 kernel uses: mbarrier, TMA
 // (cp.async.bulk.tensor, never with cluster multicast), tcgen05 (TMEM alloc, st/ld, mma, commit)
-// and the acquire/release global accesses of the stream-K fix-up.
+// and the slot accesses of the stream-K fix-up.
 //
 // Every wait in here is BOUNDED: it polls, and once a wall-clock limit has passed (or another
 // thread of the CTA has raised the shared abort word) it returns false instead of spinning on.
@@ -162,14 +162,16 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr) {
          ((uint64_t)2 << 61);
 }
 
-// ------------------------------------------------------------------------------------ global flags
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+// ------------------------------------------------------------------------------------ partial-tile slots
+// 4-byte relaxed accesses at GPU scope (served by L2, never a stale L1 line); an aligned 4-byte access is
+// single-copy atomic, so a slot is seen either idle or fully written.
+__device__ __forceinline__ void st_slot(uint32_t *p, uint32_t value) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(value) : "memory");
 }
-__device__ __forceinline__ void st_release_gpu(uint32_t *p, uint32_t v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ uint32_t ld_slot(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
 // named barrier among a subset of warps

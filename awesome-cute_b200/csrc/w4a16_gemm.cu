@@ -63,11 +63,10 @@ bool encode(CUtensorMap *map, CUtensorMapDataType dt, int rank, const void *base
   return true;
 }
 
-// Per (device, stream) state: scratch and flags of the stream-K fix-up, the status word.
+// Per (device, stream) state: scratch of the stream-K fix-up, the status word.
 struct StreamCtx {
-  float *partials = nullptr;
-  size_t partial_floats = 0;
-  uint32_t *flags = nullptr;  // [MAX_GRID][4], all zero between launches
+  uint32_t *partials = nullptr;  // fp32 partial-tile slots, all PARTIAL_IDLE (0xff bytes) between launches
+  size_t partial_slots = 0;
   int *status = nullptr;
 };
 constexpr int MAX_GRID = 256;
@@ -87,23 +86,22 @@ int sm_count(int dev) {
 }
 
 // Must be called with g_mu held.  Grows the partial-tile scratch when a launch needs more.
-StreamCtx *get_ctx(int dev, cudaStream_t stream, size_t need_floats) {
+StreamCtx *get_ctx(int dev, cudaStream_t stream, size_t need_slots) {
   StreamCtx &c = g_ctx[{dev, stream}];
-  if (!c.flags) {
-    if (!cuda_ok(cudaMalloc(&c.flags, sizeof(uint32_t) * 4 * MAX_GRID), "cudaMalloc(flags)")) return nullptr;
+  if (!c.status) {
     if (!cuda_ok(cudaMalloc(&c.status, sizeof(int)), "cudaMalloc(status)")) return nullptr;
-    if (!cuda_ok(cudaMemset(c.flags, 0, sizeof(uint32_t) * 4 * MAX_GRID), "cudaMemset(flags)")) return nullptr;
     if (!cuda_ok(cudaMemset(c.status, 0, sizeof(int)), "cudaMemset(status)")) return nullptr;
   }
-  if (c.partial_floats < need_floats) {
+  if (c.partial_slots < need_slots) {
     if (c.partials) {
       if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return nullptr;
       cudaFree(c.partials);
       c.partials = nullptr;
-      c.partial_floats = 0;
+      c.partial_slots = 0;
     }
-    if (!cuda_ok(cudaMalloc(&c.partials, sizeof(float) * need_floats), "cudaMalloc(partials)")) return nullptr;
-    c.partial_floats = need_floats;
+    if (!cuda_ok(cudaMalloc(&c.partials, sizeof(uint32_t) * need_slots), "cudaMalloc(partials)")) return nullptr;
+    if (!cuda_ok(cudaMemset(c.partials, 0xff, sizeof(uint32_t) * need_slots), "cudaMemset(partials)")) return nullptr;
+    c.partial_slots = need_slots;
   }
   return &c;
 }
@@ -186,7 +184,6 @@ int launch_tc(const Problem &pr) {
   StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 128 * w4a16::TILE_N);
   if (!ctx) return W4A16_ERR_CUDA;
   p.partials = ctx->partials;
-  p.flags = ctx->flags;
   p.status = ctx->status;
   kern<<<grid, Cfg::THREADS, smem, pr.stream>>>(tmB, tmA, tmS, p);
   if (!cuda_ok(cudaGetLastError(), "kernel launch")) return W4A16_ERR_CUDA;
@@ -317,20 +314,22 @@ extern "C" int w4a16_device_status(int dev, void *stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return W4A16_ERR_CUDA;
   int *status = nullptr;
-  uint32_t *flags = nullptr;
+  uint32_t *partials = nullptr;
+  size_t slots = 0;
   {
     std::lock_guard<std::mutex> lock(g_mu);
     auto it = g_ctx.find({dev, st});
     if (it == g_ctx.end()) return W4A16_OK;  // nothing was ever launched here
     status = it->second.status;
-    flags = it->second.flags;
+    partials = it->second.partials;
+    slots = it->second.partial_slots;
   }
   int word = 0;
   if (!cuda_ok(cudaMemcpy(&word, status, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy(status)")) return W4A16_ERR_CUDA;
   if (word == 0) return W4A16_OK;
   if (!cuda_ok(cudaMemset(status, 0, sizeof(int)), "cudaMemset(status)")) return W4A16_ERR_CUDA;
-  // a kernel that gave up may have left fix-up flags raised
-  if (!cuda_ok(cudaMemset(flags, 0, sizeof(uint32_t) * 4 * MAX_GRID), "cudaMemset(flags)")) return W4A16_ERR_CUDA;
+  // a kernel that gave up may have left partial-tile slots written
+  if (partials && !cuda_ok(cudaMemset(partials, 0xff, sizeof(uint32_t) * slots), "cudaMemset(partials)")) return W4A16_ERR_CUDA;
   g_last_error = "device-side wait timed out at site " + std::to_string(word >> 8);
   return W4A16_ERR_TIMEOUT;
 }

@@ -28,9 +28,11 @@
 // Work split: stream-K.  The (tile, k-step) space is linearised tile-major, n fastest
 // (marlin_cute_trait.h:278-286 uses the same order) and cut into equal contiguous ranges, one per CTA.
 // A tile cut between CTAs is finished by the CTA that holds its k-step 0; the others store their fp32
-// partial tile to library-owned scratch and raise a flag (release); the finisher lowers it again after
-// reading, so the flags are all zero between launches (the contract the reference's lock array has,
-// marlin_cute_trait.h:941-945) and a launch can be replayed from a CUDA graph.
+// partial tile to library-owned scratch whose idle state is a sentinel bit pattern (an all-ones NaN that
+// no accumulator is allowed to keep): the data is its own flag, so there is no fence and no separate flag
+// round trip, and the finisher simply re-reads a slot until the sentinel is gone.  It then writes the
+// sentinel back, so the scratch is in its idle state between launches (the contract the reference's lock
+// array has, marlin_cute_trait.h:941-945) and a launch can be replayed from a CUDA graph.
 // The finisher reaches that tile LAST in its own range while the contributors reach it FIRST in theirs,
 // so in practice it never waits; contributors never wait at all (no serial chain as in
 // marlin_cute_trait.h:935-950).  The finisher's wait is bounded like every other wait in the kernel.
@@ -43,6 +45,7 @@ constexpr int TILE_N = 128;                         // weight columns per tile =
 constexpr int EPI_WARPS = 4;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
 constexpr int STATUS_TIMEOUT = 4;                   // == W4A16_ERR_TIMEOUT
+constexpr uint32_t PARTIAL_IDLE = 0xffffffffu;      // idle state of a partial-tile slot (a NaN never stored as data)
 
 // Optional phase trace (compile with -DW4A16_TRACE): [cta][16] globaltimer stamps.
 #ifdef W4A16_TRACE
@@ -74,8 +77,7 @@ struct Params {
   int a_box3d;                          // 1: tmA is the 3-D view (one box per stage), 0: 2-D (one box per 64 k)
   const __half *s;                      // scales (read directly by the epilogue when per-channel)
   __half *C;
-  float *partials;                      // [gridDim.x][TM][128] fp32 partial tiles (stream-K fix-up)
-  uint32_t *flags;                      // [gridDim.x][4], one per epilogue warp; zero between launches
+  uint32_t *partials;                   // [gridDim.x][TM][128] fp32 partial tiles; PARTIAL_IDLE between launches
   int *status;                          // 0, or STATUS_TIMEOUT | (site << 8)
 };
 
@@ -94,17 +96,24 @@ struct Config {
   static constexpr int STAGE_BYTES = W_BYTES + A_BYTES + S_BYTES;
   static constexpr int ACC_STRIDE = TM < 32 ? 32 : TM;       // TMEM columns between the two accumulators
   static constexpr int WBUF_COL0 = 2 * ACC_STRIDE;
-  static constexpr int WBUF_COLS = KS / 2;                   // fp16 pairs per lane per stage
+  // The dequant -> MMA hand-off unit (sub-step) can be finer than the TMA stage; measured on B200 the two
+  // dequant sets then collide on the same stage and decode runs ~10 % slower, so it is the whole stage.
+  static constexpr int SUBK = KS;
+  static constexpr int SUBS = KS / SUBK;                     // sub-steps per stage
+  static constexpr int WBUF_COLS = SUBK / 2;                 // fp16 pairs per lane per sub-step
   static constexpr int TMEM_COLS = 512;
   static constexpr int WBUFS_RAW = (TMEM_COLS - WBUF_COL0) / WBUF_COLS;
-  static constexpr int WBUFS = WBUFS_RAW > 4 ? 4 : WBUFS_RAW;  // TMEM operand ring depth
+  static constexpr int WBUFS = WBUFS_RAW > 8 ? 8 : WBUFS_RAW;  // TMEM operand ring depth
   static_assert(WBUFS >= 2, "TMEM budget");
   static constexpr int BAR_BYTES = 1024;
   static constexpr int SMEM_MAX = 227 * 1024;
   static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static_assert(STAGES >= 3, "ring too shallow");
-  static constexpr int NDQ = 8;                              // dequant warps: two sets of four
+  // Two sets measured best on B200: a third adds eligible warps (+5 % on the largest decode shapes) but
+  // costs registers (spills at TM = 128) and start-up time on small ones.
+  static constexpr int NSETS = 2;                            // dequant sets taking k-stages round-robin
+  static constexpr int NDQ = 4 * NSETS;                      // dequant warps: NSETS sets of four
   static constexpr int THREADS = (NDQ + EPI_WARPS + 2) * 32;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024 /*align slack*/;
 };
@@ -112,8 +121,8 @@ struct Config {
 struct Bars {  // lives in shared memory
   uint64_t full[12];
   uint64_t empty[12];
-  uint64_t wfull[4];
-  uint64_t wempty[4];
+  uint64_t wfull[8];
+  uint64_t wempty[8];
   uint64_t accfull[2];
   uint64_t accempty[2];
   uint64_t drain;
@@ -204,7 +213,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     if (lane == 0) {
       for (int i = 0; i < S; ++i) {
         mbar_init(smem_u32(&bars->full[i]), 1);
-        mbar_init(smem_u32(&bars->empty[i]), 4 + 1);      // 4 dequant warps + the MMA commit
+        mbar_init(smem_u32(&bars->empty[i]), 4 * Cfg::SUBS + 1);  // 4 dequant warps per sub-step + the MMA commit
       }
       for (int i = 0; i < Cfg::WBUFS; ++i) {
         mbar_init(smem_u32(&bars->wfull[i]), 4);
@@ -249,7 +258,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
   if (warp < NDQ) {
     // =========================================================== dequant warps
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may touch
-    const int set = warp >> 2;                 // the two sets alternate k-stages
+    const int set = warp >> 2;                 // the sets take k-stages round-robin
     const int row = quad * 32 + lane;          // weight column within the tile = TMEM lane
     const int nr = row & 63, blk = row >> 6;
     const int j = nr >> 4, r8 = nr & 7;
@@ -266,25 +275,24 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16) + Cfg::WBUF_COL0;
 
     long long d_full = 0, d_wempty = 0, d_work = 0;
-    const int nsteps = it_end - it_begin;
-    for (int step = set; step < nsteps; step += 2) {
-      const int st = step % S, wb = step % Cfg::WBUFS;
+    const int nsubs = (it_end - it_begin) * Cfg::SUBS;
+    for (int g = set; g < nsubs; g += Cfg::NSETS) {      // g: this CTA's running sub-step number
+      const int step = g / Cfg::SUBS, sub = g % Cfg::SUBS;
+      const int st = step % S, wb = g % Cfg::WBUFS;
       const long long c0 = W4A16_CLK();
       if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort)) { give_up(p, abort, 1); break; }
       const long long c1 = W4A16_CLK();
-      if (warp == 0 && step == 0) W4A16_STAMP(2);   // first stage landed
-      if (!warp_wait(smem_u32(&bars->wempty[wb]), ((step / Cfg::WBUFS) & 1) ^ 1, abort)) { give_up(p, abort, 2); break; }
-      tc_fence_after();
-      const long long c2 = W4A16_CLK();
+      if (warp == 0 && g == 0) W4A16_STAMP(2);   // first stage landed
       d_full += c1 - c0;
-      d_wempty += c2 - c1;
-      const uint32_t wbase = sW_u + st * Cfg::W_BYTES;
+      const uint32_t wbase = sW_u + st * Cfg::W_BYTES + sub * (Cfg::SUBK / 16) * 1024;
+      __half2 sc = *reinterpret_cast<const __half2 *>(&one2);
+      bool buf_ok = true;
 #pragma unroll
-      for (int half = 0; half < Cfg::KCHUNKS; ++half) {
-        __half2 sc = *reinterpret_cast<const __half2 *>(&one2);
-        if (GROUPED) {
+      for (int half = 0; half < Cfg::SUBK / 64; ++half) {
+        if (GROUPED && (half & 1) == 0) {   // a new 128-k group starts every second 64-k chunk
+          const int grow = Cfg::SUBK >= 128 ? sub * (Cfg::SUBK / 128) + (half >> 1) : 0;
           uint16_t sv;
-          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sS_u + st * Cfg::S_BYTES + (half >> 1) * (TILE_N * 2) + s_off));
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sS_u + st * Cfg::S_BYTES + grow * (TILE_N * 2) + s_off));
           sc = __half2half2(__ushort_as_half(sv));
         }
         uint32_t v[32];
@@ -297,8 +305,18 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
             dequant_word<GROUPED>(w >> shift, sc, v[r * 8 + t], v[r * 8 + 4 + t]);
           }
         }
+        if (half == 0) {
+          // the TMEM operand buffer is needed only now: the first chunk was converted while the MMA that
+          // last read this buffer was still running
+          const long long c2 = W4A16_CLK();
+          buf_ok = warp_wait(smem_u32(&bars->wempty[wb]), ((g / Cfg::WBUFS) & 1) ^ 1, abort);
+          tc_fence_after();
+          d_wempty += W4A16_CLK() - c2;
+          if (!buf_ok) break;
+        }
         tmem_st_32x32b_x32(t_lane + wb * Cfg::WBUF_COLS + half * 32, v);
       }
+      if (!buf_ok) { give_up(p, abort, 2); break; }
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -306,8 +324,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
         mbar_arrive(smem_u32(&bars->wfull[wb]));
         mbar_arrive(smem_u32(&bars->empty[st]));
       }
-      d_work += W4A16_CLK() - c2;
-      if (warp == 0 && step == 0) W4A16_STAMP(3);   // first operand tile in TMEM
+      d_work += W4A16_CLK() - c1;
+      if (warp == 0 && g == 0) W4A16_STAMP(3);   // first operand tile in TMEM
     }
     if (warp == 0) {
       W4A16_STAMP(4);                               // last dequant of set 0
@@ -315,8 +333,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     }
   } else if (warp < NDQ + EPI_WARPS) {
     // =========================================================== epilogue warps
-    // Each warp serves its own TMEM lane quadrant = 32 weight columns, end to end, and publishes its
-    // own flag, so the four warps never have to meet.
+    // Each warp serves its own TMEM lane quadrant = 32 weight columns, end to end (its partial-tile slots
+    // carry their own flags), so the four warps never have to meet.
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
@@ -338,47 +356,54 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       if (!warp_wait(smem_u32(&bars->accfull[acc]), (seg >> 1) & 1, abort)) { give_up(p, abort, 3); break; }
       tc_fence_after();
       if (warp == NDQ) { if (seg == 0) W4A16_STAMP(5); W4A16_STAMP(6); }   // first / last accumulator ready
-      if (ncontrib > 0) {
-        // lane i polls contributor i (+32, ...): all flags are in flight at once
-        bool ok = true;
-        const uint64_t t0 = globaltimer_ns();
-        for (int c = (int)blockIdx.x + 1 + lane; c <= last_contrib && ok; c += 32) {
-          uint32_t i = 0;
-          while (ld_acquire_gpu(p.flags + 4 * c + quad) == 0u) {
-            if ((++i & 0x3f) == 0 && (*abort || globaltimer_ns() - t0 > WAIT_LIMIT_NS)) { ok = false; break; }
-          }
-        }
-        if (!__all_sync(0xffffffffu, ok)) { give_up(p, abort, 4); break; }
-        __threadfence();   // the other lanes read what the polling lane's acquire made visible
-        if (warp == NDQ) W4A16_STAMP(7);   // contributors' flags seen
-      }
-      float *part = p.partials + ((size_t)blockIdx.x * TM) * TILE_N + row;
+      uint32_t *part = p.partials + ((size_t)blockIdx.x * TM) * TILE_N + row;
+      bool ok = true;
+      const uint64_t t0 = ncontrib > 0 ? globaltimer_ns() : 0ull;
+      constexpr int FLY = TM <= 32 ? 4 : 2;   // contributors whose slices are in flight together
 #pragma unroll 1
-      for (int c0 = 0; c0 < TM; c0 += 16) {
+      for (int c0 = 0; c0 < TM && ok; c0 += 16) {
         uint32_t v[16];
         tmem_ld_32x32b_x16(t_lane + acc * Cfg::ACC_STRIDE + c0, v);
         tc_wait_ld();
         if (!finisher) {
+          // the data is its own flag: anything but the idle pattern means "written"
 #pragma unroll
-          for (int i = 0; i < 16; ++i) part[(size_t)(c0 + i) * TILE_N] = __uint_as_float(v[i]);
+          for (int i = 0; i < 16; ++i) st_slot(part + (size_t)(c0 + i) * TILE_N, v[i] == PARTIAL_IDLE ? 0x7fffffffu : v[i]);
         } else {
-          // fixed summation order (ascending contributor) keeps the result deterministic; two
-          // contributors' loads are put in flight together
-          int c = (int)blockIdx.x + 1;
-          for (; c + 1 <= last_contrib; c += 2) {
-            const float *s0 = p.partials + ((size_t)c * TM + c0) * TILE_N + row;
-            const float *s1 = s0 + (size_t)TM * TILE_N;
-            float x0[16], x1[16];
+          // fixed summation order (ascending contributor) keeps the result deterministic; FLY contributors'
+          // slices are read together and re-read until none shows the idle pattern
+          for (int c = (int)blockIdx.x + 1; c <= last_contrib && ok; c += FLY) {
+            uint32_t *src[FLY];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) { x0[i] = __ldcg(s0 + (size_t)i * TILE_N); x1[i] = __ldcg(s1 + (size_t)i * TILE_N); }
+            for (int f = 0; f < FLY; ++f)
+              src[f] = p.partials + ((size_t)min(c + f, last_contrib) * TM + c0) * TILE_N + row;
+            uint32_t x[FLY][16];
+            for (uint32_t spin = 0;; ++spin) {
+              bool up = true;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint((__uint_as_float(v[i]) + x0[i]) + x1[i]);
+              for (int f = 0; f < FLY; ++f)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) x[f][i] = ld_slot(src[f] + (size_t)i * TILE_N);
+#pragma unroll
+              for (int f = 0; f < FLY; ++f)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
+              if (__all_sync(0xffffffffu, up)) break;
+              if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > WAIT_LIMIT_NS)) { ok = false; break; }
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int f = 0; f < FLY; ++f) {
+              if (c + f <= last_contrib) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(x[f][i]));
+                  st_slot(src[f] + (size_t)i * TILE_N, PARTIAL_IDLE);   // back to idle for the next launch
+                }
+              }
+            }
           }
-          if (c <= last_contrib) {
-            const float *s0 = p.partials + ((size_t)c * TM + c0) * TILE_N + row;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(s0 + (size_t)i * TILE_N));
-          }
+          if (!ok) break;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int mm = m0 + c0 + i;
@@ -388,17 +413,11 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
           }
         }
       }
+      if (!ok) { give_up(p, abort, 4); break; }
+      if (warp == NDQ && ncontrib > 0) W4A16_STAMP(7);   // partial tiles folded in
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->accempty[acc]));
-      if (!finisher) {
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) st_release_gpu(p.flags + 4 * blockIdx.x + quad, 1u);
-      } else if (lane == 0) {
-        // every lane has read the partial tiles (the __syncwarp above): lower the flags for the next launch
-        for (int c = blockIdx.x + 1; c <= last_contrib; ++c) p.flags[4 * c + quad] = 0u;
-      }
       it += ke - kb;
       if (warp == NDQ) W4A16_STAMP(8);     // (last value wins) epilogue of the last segment done
     }
@@ -448,30 +467,35 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       if (!warp_wait(smem_u32(&bars->accempty[acc]), ((seg >> 1) & 1) ^ 1, abort)) { give_up(p, abort, 6); ok = false; break; }
       m_acc += W4A16_CLK() - ca;
       const uint32_t d_tmem = tmem + acc * Cfg::ACC_STRIDE;
-      for (int kk = kb; kk < ke; ++kk, ++step) {
-        const int st = step % S, wb = step % Cfg::WBUFS;
+      for (int kk = kb; kk < ke && ok; ++kk, ++step) {
+        const int st = step % S;
         const long long c0 = W4A16_CLK();
         if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort)) { give_up(p, abort, 7); ok = false; break; }
-        const long long c1 = W4A16_CLK();
-        if (!warp_wait(smem_u32(&bars->wfull[wb]), (step / Cfg::WBUFS) & 1, abort)) { give_up(p, abort, 8); ok = false; break; }
-        tc_fence_after();
-        const long long c2 = W4A16_CLK();
-        m_full += c1 - c0;
-        m_wfull += c2 - c1;
-        const uint32_t a_tmem = tmem + Cfg::WBUF_COL0 + wb * Cfg::WBUF_COLS;
+        m_full += W4A16_CLK() - c0;
         const uint64_t b_desc = make_smem_desc_sw128(sA_u + st * Cfg::A_BYTES);
-        if (elect_one()) {
 #pragma unroll
-          for (int q = 0; q < KS / 16; ++q) {
-            // next 64-k chunk is TM*128 bytes on; 16 k inside a 128-byte swizzle row are 32 bytes on
-            const uint64_t bd = b_desc + (uint64_t)(((q >> 2) * (TM * 128) + (q & 3) * 32) >> 4);
-            tc_mma_ts(d_tmem, a_tmem + q * 8, bd, idesc, (kk > kb || q > 0) ? 1u : 0u);
+        for (int sub = 0; sub < Cfg::SUBS; ++sub) {
+          const int g = step * Cfg::SUBS + sub, wb = g % Cfg::WBUFS;
+          const long long c1 = W4A16_CLK();
+          if (!warp_wait(smem_u32(&bars->wfull[wb]), (g / Cfg::WBUFS) & 1, abort)) { give_up(p, abort, 8); ok = false; break; }
+          tc_fence_after();
+          const long long c2 = W4A16_CLK();
+          m_wfull += c2 - c1;
+          const uint32_t a_tmem = tmem + Cfg::WBUF_COL0 + wb * Cfg::WBUF_COLS;
+          if (elect_one()) {
+#pragma unroll
+            for (int q = 0; q < Cfg::SUBK / 16; ++q) {
+              // 64-k chunks are TM*128 bytes apart; 16 k inside a 128-byte swizzle row are 32 bytes apart
+              const int qq = sub * (Cfg::SUBK / 16) + q;
+              const uint64_t bd = b_desc + (uint64_t)(((qq >> 2) * (TM * 128) + (qq & 3) * 32) >> 4);
+              tc_mma_ts(d_tmem, a_tmem + q * 8, bd, idesc, (kk > kb || qq > 0) ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&bars->wempty[wb]));
+            if (sub == Cfg::SUBS - 1) tc_commit(smem_u32(&bars->empty[st]));
           }
-          tc_commit(smem_u32(&bars->empty[st]));
-          tc_commit(smem_u32(&bars->wempty[wb]));
+          __syncwarp();
+          m_issue += W4A16_CLK() - c2;
         }
-        __syncwarp();
-        m_issue += W4A16_CLK() - c2;
         if (step == 0) W4A16_STAMP(11);    // first MMA issued
       }
       if (ok && elect_one()) tc_commit(smem_u32(&bars->accfull[acc]));

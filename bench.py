@@ -384,7 +384,7 @@ def run_ours(args):
 
 
 def run_case(args):
-    """One shape, eager launches, per-launch device time: the command profilers are pointed at.
+    """One shape, per-launch device time; with --eager the command profilers are pointed at.
     --case NxKxM[xG]  e.g. 22016x4096x16  (G = 128 default, -1 per-channel)."""
     import torch
 
@@ -402,19 +402,45 @@ def run_case(args):
     A = torch.randn((m, k), device=dev, generator=gen).half()
     C = torch.zeros((m, n), dtype=torch.half, device=dev)
     ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=dev)
-    for i in range(args.warmup):
-        pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
-    torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    for i, (a, b) in enumerate(evs):
-        a.record()
-        pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
-        b.record()
-    torch.cuda.synchronize()
+    if args.eager:
+        # plain launches, one event pair each: what a profiler is pointed at (host launch cost included)
+        for i in range(args.warmup):
+            pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for i, (a, b) in enumerate(evs):
+            a.record()
+            pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
+            b.record()
+        torch.cuda.synchronize()
+        us = sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
+        med, best = us[len(us) // 2], us[0]
+    else:
+        # the launches replayed from one CUDA graph: device time per launch without the host's launch path
+        side = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(side):
+            for i in range(max(args.warmup, 1)):
+                pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(args.steps):
+                pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
+        g.replay()
+        torch.cuda.synchronize()
+        us = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us.append(a.elapsed_time(b) * 1e3 / args.steps)
+        us.sort()
+        med, best = us[len(us) // 2], us[0]
     pkg.device_status(0)
-    us = sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
-    med = us[len(us) // 2]
-    print(json.dumps({"case": args.case, "copies": copies, "launch_us_median": med, "launch_us_min": us[0],
+    print(json.dumps({"case": args.case, "copies": copies, "mode": "eager" if args.eager else "graph",
+                      "launch_us_median": med, "launch_us_min": best,
                       "weight_gbs": n * k / 2 / (med * 1e-6) / 1e9, "tflops": 2.0 * m * n * k / (med * 1e-6) / 1e12}), flush=True)
 
 
@@ -425,7 +451,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the decode sweep and prefill extras")
-    ap.add_argument("--case", default=None, help="NxKxM[xG]: time one shape with eager launches (profiling aid)")
+    ap.add_argument("--case", default=None, help="NxKxM[xG]: time one shape only (graph replay; --eager for profilers)")
+    ap.add_argument("--eager", action="store_true", help="with --case: plain launches instead of a CUDA graph")
     args = ap.parse_args()
     if args.case:
         run_case(args)
