@@ -42,6 +42,9 @@ M_DECODE = 16
 COPIES = 3
 METRIC = "w4a16_weight_hbm_gbs_m16"
 UNIT = "GB/s"
+# DRAM bytes per launch from one ncu capture of each of the step's four kernels (mean of 26.14, 9.30, 46.68 and
+# 23.74 MB); the capture command and the per-shape figures are in profiles/decode_m16_dram_traffic.md.
+NCU_DRAM_BYTES_PER_LAUNCH = 26.47e6
 WORKLOAD = "llama2-7b linears (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)}, M=16, g128"
 
 
@@ -240,15 +243,10 @@ def run_ours(args):
     achieved = alg / (ms_per_step * 1e-3) / 1e9     # per launch == per step here (same 4 launches / same time)
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                "kernel": "w4a16_tc_kernel<16,128,grouped>", "launch_us": ms_total * 1e3 / launches,
+                "kernel": "w4a16_tc_kernel<16,256,grouped>", "launch_us": ms_total * 1e3 / launches,
                 "algorithmic_bytes_per_launch": alg / len(SHAPES)}
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):
-        try:
-            with open(traffic_file) as f:
-                roofline["traffic"] = json.load(f).get("dram_bytes_per_launch_m16_step_mean")
-        except Exception:
-            pass
+    roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH
+    roofline["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over the step's four launches (profiles/decode_m16_dram_traffic.md)"
 
     # ---- e2e: the public call with host buffers, no graph
     hA = [a.cpu().pin_memory() for a in acts]
@@ -338,7 +336,7 @@ def run_ours(args):
     gathered = None
     if world > 1:
         # the step with the fp16 outputs all-gathered along N (only where a caller asks for the full row)
-        gbufs = [torch.empty((world, M_DECODE, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
+        gbufs = [torch.empty((world * M_DECODE, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
 
         def gstep(i):
             step(i)

@@ -1,0 +1,90 @@
+"""The N > 1 path on CPU: two gloo ranks, each owning a column shard.  The CUDA operator has no CPU
+implementation, so the per-rank GEMM is stood in for by the oracle working on the rank's PACKED slice;
+what is under test is the shard slicing, the per-rank bookkeeping and the all-gather layout."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import __graft_entry__ as entry
+from oracle import oracle as orc
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _oracle_gemm(A, B, C, s, workspace):
+    gs = -1 if s.shape[0] == 1 else A.shape[1] // s.shape[0]
+    out = orc.c_gemm_packed(A.numpy(), B.numpy(), s.numpy(), gs)
+    C.copy_(torch.from_numpy(out).half())
+
+
+def _worker(rank, world, port, m, n, k, gs, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        pkg = entry.load_package()
+        A, codes, s = orc.make_problem(m, n, k, gs, seed=42)        # same on every rank
+        B, sp = pkg.pack_weights(codes), pkg.permute_scales(s)
+        layer = pkg.ColumnShardedLayer(B, sp, rank, world, "cpu")
+        At = torch.from_numpy(A)
+        local = layer.forward(At, gather=False, gemm=_oracle_gemm)
+        full = layer.forward(At, gather=True, gemm=_oracle_gemm)
+        ref = orc.c_gemm(A, codes, s, gs)
+        nl = n // world
+        ok_local = np.allclose(local.float().numpy(), ref[:, rank * nl:(rank + 1) * nl], rtol=2e-3, atol=2e-3)
+        ok_full = np.allclose(full.float().numpy(), ref, rtol=2e-3, atol=2e-3)
+        ws_zero = int(layer.workspace.abs().sum()) == 0
+        q.put((rank, ok_local, ok_full, ws_zero, tuple(full.shape)))
+    except Exception as e:  # surface the failure instead of letting the parent time out
+        q.put((rank, False, False, False, repr(e)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, m, n, k, gs):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, m, n, k, gs, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=90) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for (rank, ok_local, ok_full, ws_zero, shape) in res:
+        assert ok_local, "rank %d local shard wrong (%s)" % (rank, shape)
+        assert ok_full, "rank %d gathered output wrong" % rank
+        assert ws_zero
+        assert shape == (m, n)
+    for p in procs:
+        assert p.exitcode == 0
+
+
+def test_two_ranks_grouped():
+    _run(2, 5, 1024, 256, 128)
+
+
+def test_two_ranks_per_channel():
+    _run(2, 16, 512, 128, -1)
+
+
+def test_shard_constructor_rejects_ragged():
+    pkg = entry.load_package()
+    B = np.zeros((8, 2 * 768), np.int32)
+    sp = np.zeros((1, 768), np.float16)
+    try:
+        pkg.ColumnShardedLayer(B, sp, 0, 2, "cpu")     # 384 columns per rank: not a multiple of 256
+    except ValueError:
+        return
+    raise AssertionError("expected ValueError")
