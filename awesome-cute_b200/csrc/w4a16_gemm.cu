@@ -111,6 +111,10 @@ struct Problem {
   void *C;
   int m, n, k, groupsize, dev, sms;
   cudaStream_t stream;
+  // set only by the allocation-free entry point: caller-independent scratch that already exists
+  uint32_t *fixed_partials = nullptr;
+  int *fixed_status = nullptr;
+  size_t fixed_slots = 0;
 };
 
 template <int TM, int KS, bool GROUPED>
@@ -181,10 +185,21 @@ int launch_tc(const Problem &pr) {
       return W4A16_ERR_CUDA;
     attr_done[pr.dev] = true;
   }
-  StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 128 * w4a16::TILE_N);
-  if (!ctx) return W4A16_ERR_CUDA;
-  p.partials = ctx->partials;
-  p.status = ctx->status;
+  if (pr.fixed_partials) {
+    const size_t need = (size_t)grid * TM * w4a16::TILE_N;
+    if (need > pr.fixed_slots) {
+      g_last_error = "problem needs " + std::to_string(need) + " partial-tile slots, the built-in scratch holds " +
+                     std::to_string(pr.fixed_slots);
+      return W4A16_ERR_ARG;
+    }
+    p.partials = pr.fixed_partials;
+    p.status = pr.fixed_status;
+  } else {
+    StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 128 * w4a16::TILE_N);
+    if (!ctx) return W4A16_ERR_CUDA;
+    p.partials = ctx->partials;
+    p.status = ctx->status;
+  }
   kern<<<grid, Cfg::THREADS, smem, pr.stream>>>(tmB, tmA, tmS, p);
   if (!cuda_ok(cudaGetLastError(), "kernel launch")) return W4A16_ERR_CUDA;
   return W4A16_OK;
@@ -305,9 +320,101 @@ extern "C" int w4a16_marlin_gemm_simt(const void *A, const void *B, void *C, con
                     static_cast<cudaStream_t>(stream), thread_k, thread_n, sms, max_par);
 }
 
+// ---- allocation-free variant ---------------------------------------------------------------------------------
+// Scratch of the stream-K fix-up as a file-scope device array: it exists as soon as the library is loaded on a
+// device (5 MiB of every GPU that loads it, until the process exits) and is shared by every call.
+constexpr int BUILTIN_MAX_M = 64;                                    // batch rows (partial tiles are TM <= 64 wide)
+constexpr size_t BUILTIN_SLOTS = (size_t)160 * BUILTIN_MAX_M * w4a16::TILE_N;   // up to 160 CTAs: 1 310 720 slots
+static __device__ __align__(256) uint32_t g_builtin_partials[BUILTIN_SLOTS];
+static __device__ __align__(256) int g_builtin_status;
+
+namespace {
+struct BuiltinScratch {
+  uint32_t *partials = nullptr;   // DEVICE addresses of the two symbols above, per device
+  int *status = nullptr;
+  bool ready = false;
+};
+BuiltinScratch g_builtin[64];
+
+// Once per device, with that device current.  In host code `g_builtin_partials` is only a stand-in for the
+// symbol, not a device address: the address has to be asked for.  Called with g_mu held.
+int builtin_setup(int dev, cudaStream_t stream) {
+  BuiltinScratch &b = g_builtin[dev];
+  if (b.ready) return W4A16_OK;
+  int cur = -1;
+  if (!cuda_ok(cudaGetDevice(&cur), "cudaGetDevice")) return W4A16_ERR_CUDA;
+  if (cur != dev) {
+    g_last_error = "device " + std::to_string(dev) + " must be the current device (current is " + std::to_string(cur) + ")";
+    return W4A16_ERR_ARG;
+  }
+  void *pp = nullptr, *ps = nullptr;
+  if (!cuda_ok(cudaGetSymbolAddress(&pp, g_builtin_partials), "cudaGetSymbolAddress(partials)")) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaGetSymbolAddress(&ps, g_builtin_status), "cudaGetSymbolAddress(status)")) return W4A16_ERR_CUDA;
+  // idle pattern in every slot, status clear; finished before any kernel of any stream can touch them
+  if (!cuda_ok(cudaMemsetAsync(pp, 0xff, sizeof(uint32_t) * BUILTIN_SLOTS, stream), "cudaMemsetAsync(partials)")) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaMemsetAsync(ps, 0, sizeof(int), stream), "cudaMemsetAsync(status)")) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return W4A16_ERR_CUDA;
+  b.partials = static_cast<uint32_t *>(pp);
+  b.status = static_cast<int *>(ps);
+  b.ready = true;
+  return W4A16_OK;
+}
+}  // namespace
+
+extern "C" int w4a16_marlin_gemm_builtin_scratch(const void *A, const void *B, void *C, const void *s, int prob_m,
+                                                 int prob_n, int prob_k, void *workspace, int groupsize, int dev,
+                                                 void *stream, int thread_k, int thread_n, int sms, int max_par) {
+  (void)max_par;
+  (void)workspace;
+  if (prob_m < 0 || prob_n < 0 || prob_k < 0) return W4A16_ERR_ARG;
+  const int chk = check_problem(prob_m, prob_n, prob_k, groupsize, thread_k, thread_n);
+  if (chk == -1) return W4A16_OK;
+  if (chk != W4A16_OK) return chk;
+  if (prob_m > BUILTIN_MAX_M) {
+    g_last_error = "m = " + std::to_string(prob_m) + " exceeds the built-in scratch limit of " + std::to_string(BUILTIN_MAX_M) +
+                   " rows; use w4a16_marlin_gemm";
+    return W4A16_ERR_ARG;
+  }
+  if (!A || !B || !C || !s) return W4A16_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(s)) & 15)
+    return W4A16_ERR_ARG;
+  if (dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Problem pr{A, B, s, C, prob_m, prob_n, prob_k, groupsize, dev, sms, st};
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    const int rc = builtin_setup(dev, st);
+    if (rc != W4A16_OK) return rc;
+    pr.fixed_partials = g_builtin[dev].partials;
+    pr.fixed_status = g_builtin[dev].status;
+    pr.fixed_slots = BUILTIN_SLOTS;
+  }
+  return dispatch_tc(pr);
+}
+
 extern "C" int w4a16_workspace_ints(int prob_n, int max_par) {
   if (prob_n < 0 || max_par < 0) return 0;
   return prob_n / 128 * max_par;
+}
+
+// status word of the allocation-free variant (shared by all streams of the device)
+static int builtin_status(int dev) {
+  uint32_t *partials = nullptr;
+  int *status = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (dev < 0 || dev >= 64 || !g_builtin[dev].ready) return W4A16_OK;
+    partials = g_builtin[dev].partials;
+    status = g_builtin[dev].status;
+  }
+  int word = 0;
+  if (!cuda_ok(cudaMemcpy(&word, status, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy(status)")) return W4A16_ERR_CUDA;
+  if (word == 0) return W4A16_OK;
+  if (!cuda_ok(cudaMemset(status, 0, sizeof(int)), "cudaMemset(status)")) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaMemset(partials, 0xff, sizeof(uint32_t) * BUILTIN_SLOTS), "cudaMemset(partials)")) return W4A16_ERR_CUDA;
+  g_last_error = "device-side wait timed out at site " + std::to_string(word >> 8) + " (built-in scratch variant)";
+  return W4A16_ERR_TIMEOUT;
 }
 
 extern "C" int w4a16_device_status(int dev, void *stream) {
@@ -316,17 +423,21 @@ extern "C" int w4a16_device_status(int dev, void *stream) {
   int *status = nullptr;
   uint32_t *partials = nullptr;
   size_t slots = 0;
+  bool launched_here = false;
   {
     std::lock_guard<std::mutex> lock(g_mu);
     auto it = g_ctx.find({dev, st});
-    if (it == g_ctx.end()) return W4A16_OK;  // nothing was ever launched here
-    status = it->second.status;
-    partials = it->second.partials;
-    slots = it->second.partial_slots;
+    if (it != g_ctx.end()) {
+      launched_here = true;
+      status = it->second.status;
+      partials = it->second.partials;
+      slots = it->second.partial_slots;
+    }
   }
+  if (!launched_here) return builtin_status(dev);  // no library-allocated scratch on this (device, stream)
   int word = 0;
   if (!cuda_ok(cudaMemcpy(&word, status, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy(status)")) return W4A16_ERR_CUDA;
-  if (word == 0) return W4A16_OK;
+  if (word == 0) return builtin_status(dev);
   if (!cuda_ok(cudaMemset(status, 0, sizeof(int)), "cudaMemset(status)")) return W4A16_ERR_CUDA;
   // a kernel that gave up may have left partial-tile slots written
   if (partials && !cuda_ok(cudaMemset(partials, 0xff, sizeof(uint32_t) * slots), "cudaMemset(partials)")) return W4A16_ERR_CUDA;

@@ -49,6 +49,35 @@ int w4a16_marlin_gemm(const void *A, const void *B, void *C, const void *s, int 
                       void *workspace, int groupsize, int dev, void *stream, int thread_k, int thread_n, int sms,
                       int max_par);
 
+/*
+ * The same GEMM for callers that cannot let a library allocate device memory.  It has no counterpart in the
+ * reference (whose launcher never needs scratch beyond the caller's workspace, because it keeps fp16 partial
+ * sums in C).
+ *
+ * Who needs it: a process whose framework allocator has already reserved the whole device, so that a raw
+ * cudaMalloc made by this library fails with out-of-memory or eats into memory the framework believes it
+ * owns; a latency-critical loop, where cudaMalloc / cudaFree stall every stream of the device while they run;
+ * and callers whose memory budget is audited, where a hidden per-stream cache of 17 MB is not acceptable.
+ * w4a16_marlin_gemm allocates its fix-up scratch on the first call of every (device, stream) pair; this entry
+ * point never calls cudaMalloc, cudaFree or any allocating routine.  Its scratch is a 5 MiB array compiled
+ * into the library (every GPU that loads the library holds it until the process exits).
+ *
+ * Arguments, results and return codes are those of w4a16_marlin_gemm, with these differences:
+ *   - prob_m <= 64 only, and at most 160 CTAs (any sm_100 part today); beyond that it returns W4A16_ERR_ARG and
+ *     w4a16_last_cuda_error() says which limit was hit.  Larger batches must use w4a16_marlin_gemm.
+ *   - The first call on a device looks up the device address of the built-in array (cudaGetSymbolAddress),
+ *     puts the array into its idle state on `stream` and synchronises `stream`.  `dev` must be the current
+ *     device.  Make that first call before any stream capture begins.
+ *   - All calls on one device share the one array.  Each call leaves it in the idle state, so back-to-back
+ *     calls on ONE stream are fine; two calls that overlap on the GPU (different streams, or different host
+ *     threads feeding different streams) race on it and produce garbage.  Serialise them.
+ *   - A bounded wait that runs out is reported by w4a16_device_status(dev, stream), which then also restores
+ *     the idle state.
+ */
+int w4a16_marlin_gemm_builtin_scratch(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n,
+                                      int prob_k, void *workspace, int groupsize, int dev, void *stream, int thread_k,
+                                      int thread_n, int sms, int max_par);
+
 /* Size rule of the caller's lock array: n / 128 * max_par  (gemm/marlin_gemm/marlin_gemm.cpp:29-31,
  * gemm/marlin_gemm/marlin.py:85). */
 int w4a16_workspace_ints(int prob_n, int max_par);
