@@ -115,6 +115,9 @@ struct Problem {
   uint32_t *fixed_partials = nullptr;
   int *fixed_status = nullptr;
   size_t fixed_slots = 0;
+  // set only by the bounded-wait self-test: launch CTA 0 alone, so that it waits for partial tiles nobody writes
+  bool orphan_finisher = false;
+  uint64_t wait_ns = w4a16::WAIT_LIMIT_NS;
 };
 
 template <int TM, int KS, bool GROUPED>
@@ -144,6 +147,12 @@ int launch_tc(const Problem &pr) {
   grid = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
   p.s = static_cast<const __half *>(pr.s);
   p.C = static_cast<__half *>(pr.C);
+  p.wait_ns = pr.wait_ns;
+  if (pr.orphan_finisher) {
+    if (p.k_iters < 2) return W4A16_ERR_ARG;
+    p.iters_per_cta = p.k_iters / 2;   // tile 0 is cut in two ...
+    grid = 1;                          // ... and only the CTA that finishes it is launched
+  }
 
   CUtensorMap tmB, tmA, tmS;
   {  // weights: int32 [k/16][2n] viewed as [k/16][2n/32][32] so a 128-byte inner box can be swizzled
@@ -311,6 +320,46 @@ extern "C" int w4a16_marlin_gemm(const void *A, const void *B, void *C, const vo
                                  int thread_n, int sms, int max_par) {
   return gemm_entry(false, A, B, C, s, prob_m, prob_n, prob_k, workspace, groupsize, dev,
                     static_cast<cudaStream_t>(stream), thread_k, thread_n, sms, max_par);
+}
+
+// The GEMM with HOST activations and HOST output: copy in, multiply, copy out, all enqueued on `stream`.
+extern "C" int w4a16_marlin_gemm_host(const void *A_host, const void *B, void *C_host, const void *s, int prob_m,
+                                      int prob_n, int prob_k, void *workspace, int groupsize, int dev, void *stream,
+                                      void *A_stage, void *C_stage) {
+  if (prob_m < 0 || prob_n < 0 || prob_k < 0) return W4A16_ERR_ARG;
+  int tk = -1, tn = -1;
+  const int chk = check_problem(prob_m, prob_n, prob_k, groupsize, tk, tn);
+  if (chk == -1) return W4A16_OK;
+  if (chk != W4A16_OK) return chk;
+  if (!A_host || !C_host || !A_stage || !C_stage) return W4A16_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!cuda_ok(cudaMemcpyAsync(A_stage, A_host, sizeof(__half) * (size_t)prob_m * prob_k, cudaMemcpyHostToDevice, st),
+               "cudaMemcpyAsync(A)"))
+    return W4A16_ERR_CUDA;
+  const int rc = gemm_entry(false, A_stage, B, C_stage, s, prob_m, prob_n, prob_k, workspace, groupsize, dev, st, -1, -1,
+                            -1, 16);
+  if (rc != W4A16_OK) return rc;
+  if (!cuda_ok(cudaMemcpyAsync(C_host, C_stage, sizeof(__half) * (size_t)prob_m * prob_n, cudaMemcpyDeviceToHost, st),
+               "cudaMemcpyAsync(C)"))
+    return W4A16_ERR_CUDA;
+  return W4A16_OK;
+}
+
+// Self-test of the bounded waits: the GEMM is set up so that the CTA finishing tile 0 expects a partial tile
+// from a CTA that is never launched.  Nothing faults or spins on: after limit_ms the kernel records a status,
+// unwinds and returns, and w4a16_device_status reports W4A16_ERR_TIMEOUT.  C is left undefined.
+extern "C" int w4a16_selftest_unanswered_wait(const void *A, const void *B, void *C, const void *s, int prob_m,
+                                              int prob_n, int prob_k, int groupsize, int dev, void *stream,
+                                              int limit_ms) {
+  int tk = -1, tn = -1;
+  if (prob_m <= 0 || prob_n <= 0 || prob_k <= 0 || limit_ms <= 0 || limit_ms > 5000) return W4A16_ERR_ARG;
+  const int chk = check_problem(prob_m, prob_n, prob_k, groupsize, tk, tn);
+  if (chk != W4A16_OK) return chk;
+  if (!A || !B || !C || !s || dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  Problem pr{A, B, s, C, prob_m, prob_n, prob_k, groupsize, dev, -1, static_cast<cudaStream_t>(stream)};
+  pr.orphan_finisher = true;
+  pr.wait_ns = (uint64_t)limit_ms * 1000000ull;
+  return dispatch_tc(pr);
 }
 
 extern "C" int w4a16_marlin_gemm_simt(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n,

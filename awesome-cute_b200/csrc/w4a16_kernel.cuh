@@ -79,6 +79,7 @@ struct Params {
   __half *C;
   uint32_t *partials;                   // [gridDim.x][TM][128] fp32 partial tiles; PARTIAL_IDLE between launches
   int *status;                          // 0, or STATUS_TIMEOUT | (site << 8)
+  uint64_t wait_ns;                     // every device-side wait gives up after this long (WAIT_LIMIT_NS by default)
 };
 
 // Tile configuration.  TM = batch tile (UMMA N); KS = k per pipeline stage.  The stage is the unit of
@@ -133,8 +134,8 @@ static_assert(sizeof(Bars) <= 1024, "barrier block");
 
 // A wait whose verdict is the same in every lane of the warp (the tcgen05 ld/st that follow are
 // warp-collective).
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *abort) {
-  const bool ok = sm100::mbar_wait(bar, parity, abort, WAIT_LIMIT_NS);
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *abort, uint64_t limit_ns) {
+  const bool ok = sm100::mbar_wait(bar, parity, abort, limit_ns);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -280,7 +281,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       const int step = g / Cfg::SUBS, sub = g % Cfg::SUBS;
       const int st = step % S, wb = g % Cfg::WBUFS;
       const long long c0 = W4A16_CLK();
-      if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort)) { give_up(p, abort, 1); break; }
+      if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort, p.wait_ns)) { give_up(p, abort, 1); break; }
       const long long c1 = W4A16_CLK();
       if (warp == 0 && g == 0) W4A16_STAMP(2);   // first stage landed
       d_full += c1 - c0;
@@ -309,7 +310,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
           // the TMEM operand buffer is needed only now: the first chunk was converted while the MMA that
           // last read this buffer was still running
           const long long c2 = W4A16_CLK();
-          buf_ok = warp_wait(smem_u32(&bars->wempty[wb]), ((g / Cfg::WBUFS) & 1) ^ 1, abort);
+          buf_ok = warp_wait(smem_u32(&bars->wempty[wb]), ((g / Cfg::WBUFS) & 1) ^ 1, abort, p.wait_ns);
           tc_fence_after();
           d_wempty += W4A16_CLK() - c2;
           if (!buf_ok) break;
@@ -353,7 +354,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
         const int c32 = row & 31;  // per-channel scales are permuted inside 32-column blocks (marlin.py:52-54)
         sch = p.s[n0 + row - c32 + 8 * ((c32 & 7) >> 1) + 2 * (c32 >> 3) + (c32 & 1)];
       }
-      if (!warp_wait(smem_u32(&bars->accfull[acc]), (seg >> 1) & 1, abort)) { give_up(p, abort, 3); break; }
+      if (!warp_wait(smem_u32(&bars->accfull[acc]), (seg >> 1) & 1, abort, p.wait_ns)) { give_up(p, abort, 3); break; }
       tc_fence_after();
       if (warp == NDQ) { if (seg == 0) W4A16_STAMP(5); W4A16_STAMP(6); }   // first / last accumulator ready
       uint32_t *part = p.partials + ((size_t)blockIdx.x * TM) * TILE_N + row;
@@ -389,7 +390,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
 #pragma unroll
                 for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
               if (__all_sync(0xffffffffu, up)) break;
-              if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > WAIT_LIMIT_NS)) { ok = false; break; }
+              if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > p.wait_ns)) { ok = false; break; }
             }
             if (!ok) break;
 #pragma unroll
@@ -429,7 +430,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     for (; pro_step < nsteps; ++pro_step) {
       const int st = pro_step % S;
       const long long c0 = W4A16_CLK();
-      if (!warp_wait(smem_u32(&bars->empty[st]), ((pro_step / S) & 1) ^ 1, abort)) { give_up(p, abort, 5); break; }
+      if (!warp_wait(smem_u32(&bars->empty[st]), ((pro_step / S) & 1) ^ 1, abort, p.wait_ns)) { give_up(p, abort, 5); break; }
       const long long c1 = W4A16_CLK();
       c_wait += c1 - c0;
       if (elect_one()) issue_stage(st, pro_nidx, pro_m0, pro_kk);
@@ -464,20 +465,20 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       const int ke = min(p.k_iters, kb + (it_end - it));
       const int acc = seg & 1;
       const long long ca = W4A16_CLK();
-      if (!warp_wait(smem_u32(&bars->accempty[acc]), ((seg >> 1) & 1) ^ 1, abort)) { give_up(p, abort, 6); ok = false; break; }
+      if (!warp_wait(smem_u32(&bars->accempty[acc]), ((seg >> 1) & 1) ^ 1, abort, p.wait_ns)) { give_up(p, abort, 6); ok = false; break; }
       m_acc += W4A16_CLK() - ca;
       const uint32_t d_tmem = tmem + acc * Cfg::ACC_STRIDE;
       for (int kk = kb; kk < ke && ok; ++kk, ++step) {
         const int st = step % S;
         const long long c0 = W4A16_CLK();
-        if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort)) { give_up(p, abort, 7); ok = false; break; }
+        if (!warp_wait(smem_u32(&bars->full[st]), (step / S) & 1, abort, p.wait_ns)) { give_up(p, abort, 7); ok = false; break; }
         m_full += W4A16_CLK() - c0;
         const uint64_t b_desc = make_smem_desc_sw128(sA_u + st * Cfg::A_BYTES);
 #pragma unroll
         for (int sub = 0; sub < Cfg::SUBS; ++sub) {
           const int g = step * Cfg::SUBS + sub, wb = g % Cfg::WBUFS;
           const long long c1 = W4A16_CLK();
-          if (!warp_wait(smem_u32(&bars->wfull[wb]), (g / Cfg::WBUFS) & 1, abort)) { give_up(p, abort, 8); ok = false; break; }
+          if (!warp_wait(smem_u32(&bars->wfull[wb]), (g / Cfg::WBUFS) & 1, abort, p.wait_ns)) { give_up(p, abort, 8); ok = false; break; }
           tc_fence_after();
           const long long c2 = W4A16_CLK();
           m_wfull += c2 - c1;

@@ -53,12 +53,41 @@ def mul(A, B, C, s, workspace, thread_k=-1, thread_n=-1, sms=-1, max_par=16, cut
     if not A.is_cuda:
         raise RuntimeError("mul() needs CUDA tensors; there is no CPU implementation of this operator.")
     dev = A.get_device()
-    stream = torch.cuda.current_stream(dev).cuda_stream
     fn = _entry or _L.w4a16_marlin_gemm
-    with torch.cuda.device(dev):
-        err = fn(_ptr(A), _ptr(B), _ptr(C), _ptr(s), prob_m, prob_n, prob_k, _ptr(workspace), groupsize, dev,
-                 ctypes.c_void_p(stream), thread_k, thread_n, sms, max_par)
-    _check(err, prob_m, prob_n, prob_k, thread_k, thread_n, groupsize)
+    if torch.cuda.current_device() == dev:
+        err = fn(A.data_ptr(), B.data_ptr(), C.data_ptr(), s.data_ptr(), prob_m, prob_n, prob_k, workspace.data_ptr(),
+                 groupsize, dev, torch.cuda.current_stream(dev).cuda_stream, thread_k, thread_n, sms, max_par)
+    else:
+        with torch.cuda.device(dev):
+            err = fn(A.data_ptr(), B.data_ptr(), C.data_ptr(), s.data_ptr(), prob_m, prob_n, prob_k,
+                     workspace.data_ptr(), groupsize, dev, torch.cuda.current_stream(dev).cuda_stream, thread_k,
+                     thread_n, sms, max_par)
+    if err:
+        _check(err, prob_m, prob_n, prob_k, thread_k, thread_n, groupsize)
+
+
+def mul_host(A_host, B, C_host, s, workspace, A_stage, C_stage):
+    """`mul` for HOST activations / outputs (pinned torch tensors): copy in, multiply, copy out, all enqueued
+    on the current stream of B's device by one call into the library.  A_stage [m, k] and C_stage [m, n] are
+    device staging tensors owned by the caller; B, s, workspace are device tensors as for `mul`.  Synchronise
+    the stream before reading C_host."""
+    prob_m, prob_k = A_host.shape
+    prob_n = C_host.shape[1]
+    groupsize = -1 if s.shape[0] == 1 else prob_k // s.shape[0]
+    if groupsize != -1 and groupsize * s.shape[0] != prob_k:
+        raise RuntimeError("k=%d not compatible with %d groups." % (prob_k, s.shape[0]))
+    if workspace.numel() < _L.w4a16_workspace_ints(prob_n, 16):
+        raise RuntimeError("workspace must be of size at least %d." % _L.w4a16_workspace_ints(prob_n, 16))
+    if A_host.is_cuda or C_host.is_cuda or not B.is_cuda:
+        raise RuntimeError("mul_host() takes host activations/outputs and device weights.")
+    dev = B.get_device()
+    if torch.cuda.current_device() != dev:
+        raise RuntimeError("device %d must be current" % dev)
+    err = _L.w4a16_marlin_gemm_host(A_host.data_ptr(), B.data_ptr(), C_host.data_ptr(), s.data_ptr(), prob_m, prob_n,
+                                    prob_k, workspace.data_ptr(), groupsize, dev,
+                                    torch.cuda.current_stream(dev).cuda_stream, A_stage.data_ptr(), C_stage.data_ptr())
+    if err:
+        _check(err, prob_m, prob_n, prob_k, -1, -1, groupsize)
 
 
 def mul_simt(A, B, C, s, workspace, thread_k=-1, thread_n=-1, sms=-1, max_par=16):

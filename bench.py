@@ -11,8 +11,9 @@ four GEMM launches that stream 101 MB of packed weights.  Weights rotate over 3 
 metric / value   weight HBM GB/s = packed-weight bytes of all ranks / time (CUDA events, max over ranks);
                  the K timed steps are replayed from one CUDA graph so the figure is the kernels', not
                  Python's launch path
-e2e              the same metric through the public call `mul()` with HOST buffers: per GEMM the
-                 activations are copied from pinned host memory and the output copied back, no graph;
+e2e              the same metric through the public call `mul_host()` (C ABI w4a16_marlin_gemm_host) with HOST
+                 buffers: per GEMM the activations are copied from pinned host memory and the output copied
+                 back inside the call, plain launches, no graph;
                  weights stay resident on the device as a layer's parameters do (marlin.py:82-83)
 roofline         HBM bound: algorithmic bytes (weights + scales + A + C) per launch / mean launch time
 cpu_baseline     the CPU oracle (dequantise + fp32 GEMM, all host threads) on one full step
@@ -252,19 +253,26 @@ def run_ours(args):
     hA = [a.cpu().pin_memory() for a in acts]
     hC = [torch.empty((M_DECODE, n), dtype=torch.half).pin_memory() for (n, _) in SHAPES]
 
+    # the step's four GEMMs are independent layers: each is issued on its own stream so that one layer's
+    # host<->device copies overlap another layer's kernel (each stream has its own library scratch)
+    lanes = [torch.cuda.Stream(device=dev) for _ in SHAPES]
+
     def e2e_step(i):
         c = i % COPIES
-        for li in range(len(SHAPES)):
-            acts[li].copy_(hA[li], non_blocking=True)
-            pkg.mul(acts[li], layers[li][0][c], outs[li], layers[li][1][c], wss[li])
-            hC[li].copy_(outs[li], non_blocking=True)
+        for li in range(len(SHAPES)):   # h2d copy of A, GEMM, d2h copy of C: one public call per GEMM
+            with torch.cuda.stream(lanes[li]):
+                pkg.mul_host(hA[li], layers[li][0][c], hC[li], layers[li][1][c], wss[li], acts[li], outs[li])
 
     for i in range(3):
         e2e_step(i)
     barrier()
     e0.record()
+    for st_ in lanes:
+        st_.wait_event(e0)
     for i in range(args.steps):
         e2e_step(i)
+    for st_ in lanes:
+        torch.cuda.current_stream().wait_stream(st_)
     e1.record()
     torch.cuda.synchronize()
     barrier()

@@ -78,6 +78,19 @@ int w4a16_marlin_gemm_builtin_scratch(const void *A, const void *B, void *C, con
                                       int prob_k, void *workspace, int groupsize, int dev, void *stream, int thread_k,
                                       int thread_n, int sms, int max_par);
 
+/*
+ * w4a16_marlin_gemm for callers whose activations and outputs live in HOST memory (pinned, for the copies to
+ * be asynchronous): enqueues on `stream` the copy of A_host [m, k] into the device staging buffer A_stage, the
+ * GEMM (automatic tiles), and the copy of the result from the device staging buffer C_stage [m, n] into
+ * C_host.  B, s, workspace, A_stage and C_stage are device pointers owned by the caller (the weights stay
+ * resident, as the reference's Layer keeps them, gemm/marlin_gemm/marlin.py:82-85).  It is the host-tensor
+ * form of the reference's  mul()  (gemm/marlin_gemm/marlin.py:11-24), which the reference only offers for
+ * device tensors.  Returns like w4a16_marlin_gemm; the caller synchronises `stream` before reading C_host.
+ */
+int w4a16_marlin_gemm_host(const void *A_host, const void *B, void *C_host, const void *s, int prob_m, int prob_n,
+                           int prob_k, void *workspace, int groupsize, int dev, void *stream, void *A_stage,
+                           void *C_stage);
+
 /* Size rule of the caller's lock array: n / 128 * max_par  (gemm/marlin_gemm/marlin_gemm.cpp:29-31,
  * gemm/marlin_gemm/marlin.py:85). */
 int w4a16_workspace_ints(int prob_n, int max_par);
@@ -87,6 +100,14 @@ int w4a16_workspace_ints(int prob_n, int max_par);
  * W4A16_ERR_CUDA.  The reference has no counterpart: its fix-up spin is unbounded
  * (include/barrier.h:85-96). */
 int w4a16_device_status(int dev, void *stream);
+
+/* Self-test of the bounded device-side waits (the reference has none: its fix-up spin is unbounded,
+ * include/barrier.h:85-96).  Launches the GEMM so that one CTA waits for a partial tile that no CTA will ever
+ * write; after limit_ms (1..5000) the kernel gives up, unwinds and returns.  The call itself returns W4A16_OK;
+ * w4a16_device_status(dev, stream) then returns W4A16_ERR_TIMEOUT and restores the scratch, after which the
+ * stream is usable as before.  C is left undefined.  Injects no GPU fault. */
+int w4a16_selftest_unanswered_wait(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n,
+                                   int prob_k, int groupsize, int dev, void *stream, int limit_ms);
 
 /* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
 const char *w4a16_last_cuda_error(void);

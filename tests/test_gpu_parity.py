@@ -185,3 +185,42 @@ def test_layer_forward_like_reference_module():
     pkg.device_status(0)
     assert tuple(out.shape) == (2, 12, n)
     check(out.view(24, n), orc.c_gemm(A, q, s, gs))
+
+
+def test_mul_host_copies_in_and_out():
+    """The host-buffer form of the call: pinned A in, pinned C out, one library call."""
+    m, n, k, gs = 16, 1024, 2048, 128
+    A, q, s = orc.make_problem(m, n, k, gs, 31)
+    _, Bt, st = pack_problem(A, q, s)
+    hA = torch.from_numpy(A).pin_memory()
+    hC = torch.zeros((m, n), dtype=torch.half).pin_memory()
+    A_stage = torch.empty((m, k), dtype=torch.half, device=DEV)
+    C_stage = torch.empty((m, n), dtype=torch.half, device=DEV)
+    ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=DEV)
+    for _ in range(2):
+        pkg.mul_host(hA, Bt, hC, st, ws, A_stage, C_stage)
+    pkg.device_status(0)
+    check(hC, orc.c_gemm(A, q, s, gs), "mul_host")
+
+
+def test_bounded_wait_runs_out_and_the_stream_survives():
+    """Failure detection without a GPU fault: a CTA waits for a partial tile nobody writes; after the limit the
+    kernel returns a status instead of hanging, and the next GEMM on the same stream is correct."""
+    import ctypes
+    import time
+    from awesome_cute_b200 import _lib
+    m, n, k, gs = 16, 256, 1024, 128
+    A, q, s = orc.make_problem(m, n, k, gs, 55)
+    At, Bt, st = pack_problem(A, q, s)
+    C = torch.zeros((m, n), dtype=torch.half, device=DEV)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream(0).cuda_stream)
+    run_mul(At, Bt, st, m, n)                     # scratch of this stream exists and is idle
+    t0 = time.time()
+    rc = _lib.lib.w4a16_selftest_unanswered_wait(p(At), p(Bt), p(C), p(st), m, n, k, gs, 0, stream, 300)
+    assert rc == _lib.OK, _lib.last_cuda_error()
+    assert _lib.lib.w4a16_device_status(0, stream) == _lib.ERR_TIMEOUT
+    assert "timed out at site 4" in _lib.last_cuda_error()
+    assert 0.25 < time.time() - t0 < 3.0          # it waited for the limit, not for ever
+    assert _lib.lib.w4a16_device_status(0, stream) == _lib.OK      # status is cleared once read
+    check(run_mul(At, Bt, st, m, n), orc.c_gemm(A, q, s, gs), "after the timeout")
