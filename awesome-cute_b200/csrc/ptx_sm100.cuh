@@ -174,6 +174,13 @@ __device__ __forceinline__ uint32_t ld_slot(const uint32_t *p) {
   return v;
 }
 
+// ------------------------------------------------------------------------------------ dependent launch
+// Programmatic dependent launch: `launch_dependents` lets the next kernel of the stream (if it was launched
+// with the programmatic-serialisation attribute) begin before this one ends; `wait` in that next kernel blocks
+// until this whole grid has finished and its writes are visible.  Both are no-ops without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // named barrier among a subset of warps
 __device__ __forceinline__ void bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

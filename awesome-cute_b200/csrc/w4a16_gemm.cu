@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <string>
@@ -21,6 +22,12 @@
 namespace {
 
 thread_local std::string g_last_error;
+
+// W4A16_PDL=0 in the environment turns programmatic dependent launch off (debugging aid)
+const bool g_use_pdl = [] {
+  const char *e = std::getenv("W4A16_PDL");
+  return !(e && e[0] == '0');
+}();
 
 bool cuda_ok(cudaError_t e, const char *what) {
   if (e == cudaSuccess) return true;
@@ -209,8 +216,21 @@ int launch_tc(const Problem &pr) {
     p.partials = ctx->partials;
     p.status = ctx->status;
   }
-  kern<<<grid, Cfg::THREADS, smem, pr.stream>>>(tmB, tmA, tmS, p);
-  if (!cuda_ok(cudaGetLastError(), "kernel launch")) return W4A16_ERR_CUDA;
+  // Programmatic dependent launch: this kernel may begin (prologue, weight prefetch) while the previous kernel of
+  // the stream is finishing; it orders itself behind that kernel with griddepcontrol.wait before it reads
+  // activations or writes anything.  Only this library's kernels signal early, so behind any other kernel the
+  // launch is an ordinary stream-ordered one.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)Cfg::THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = pr.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, tmB, tmA, tmS, p), "kernel launch")) return W4A16_ERR_CUDA;
   return W4A16_OK;
 }
 

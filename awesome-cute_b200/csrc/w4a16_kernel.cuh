@@ -193,10 +193,14 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
   // One stage of loads.  Coordinates: weights are the 3-D view [k/16][2n/32][32 int32] (box KS/16 x 8 x 32
   // words); activations [k/64][m][64] (box KS/64 x TM x 64) or, as 2-D, one 64 x TM box per 64 k; scales
   // [k/128][n] (box GROUPS x 128).
-  auto issue_stage = [&](int st, int n_idx, int m0, int kk) {
+  auto issue_weights = [&](int st, int n_idx, int kk) {   // packed weights + group scales: immutable parameters
     const uint32_t full = smem_u32(&bars->full[st]);
     mbar_expect_tx(full, STAGE_TX);
     tma_load_3d(smem_u32(sW) + st * Cfg::W_BYTES, &tmB, 0, n_idx * 8, kk * (KS / 16), full);
+    if (GROUPED) tma_load_2d(smem_u32(sS) + st * Cfg::S_BYTES, &tmS, n_idx * TILE_N, (kk * KS) / 128, full);
+  };
+  auto issue_acts = [&](int st, int m0, int kk) {         // activations: may be the previous kernel's output
+    const uint32_t full = smem_u32(&bars->full[st]);
     if (p.a_box3d) {
       tma_load_3d(smem_u32(sA) + st * Cfg::A_BYTES, &tmA, 0, m0, kk * Cfg::KCHUNKS, full);
     } else {
@@ -204,11 +208,14 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       for (int h = 0; h < Cfg::KCHUNKS; ++h)
         tma_load_2d(smem_u32(sA) + st * Cfg::A_BYTES + h * TM * 128, &tmA, kk * KS + h * 64, m0, full);
     }
-    if (GROUPED) tma_load_2d(smem_u32(sS) + st * Cfg::S_BYTES, &tmS, n_idx * TILE_N, (kk * KS) / 128, full);
   };
 
   // ---- prologue.  The producer warp initialises the barriers and puts the first ring-full of loads in
   // flight BEFORE the CTA-wide sync, so HBM latency overlaps the TMEM allocation and the sync itself.
+  // Under programmatic dependent launch this CTA may be running while the previous kernel of the stream is
+  // still finishing: the weights and scales of the first ring-full (parameters, never a kernel's output) are
+  // requested at once, everything else (activations, C, the partial-tile scratch) only after
+  // pdl_wait_prior_grid().
   int pro_step = 0, pro_tile = 0, pro_kk = 0, pro_nidx = 0, pro_m0 = 0;
   if (warp == PRODUCER_WARP) {
     if (lane == 0) {
@@ -234,21 +241,38 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     pro_kk = it_begin - pro_tile * p.k_iters;
     pro_nidx = pro_tile % p.n_tiles;
     pro_m0 = (pro_tile / p.n_tiles) * TM;
+    bar_sync(1, 64);               // barriers are initialised: the MMA warp may issue the activation loads
     const int first = min(S, it_end - it_begin);
     for (; pro_step < first; ++pro_step) {
-      if (elect_one()) issue_stage(pro_step, pro_nidx, pro_m0, pro_kk);
+      if (elect_one()) issue_weights(pro_step, pro_nidx, pro_kk);
       __syncwarp();
       if (++pro_kk == p.k_iters) {
         pro_kk = 0;
-        ++pro_tile;
         if (++pro_nidx == p.n_tiles) { pro_nidx = 0; pro_m0 += TM; }
       }
     }
+    pdl_launch_dependents();       // the next kernel may start its own prologue as SMs free up
+    pdl_wait_prior_grid();         // (the steady-state loop below issues activation loads too)
     W4A16_STAMP(9);                // first ring-full issued
   }
   if (warp == MMA_WARP) {          // the MMA warp owns TMEM
     tmem_alloc(smem_u32(&bars->tmem_base), Cfg::TMEM_COLS);
     tmem_relinquish();
+    // ... and, idle until the first operand tile exists, issues the first ring-full of ACTIVATION loads next to
+    // the producer's weight loads, once the previous kernel of the stream has finished
+    bar_sync(1, 64);
+    pdl_wait_prior_grid();
+    int tile = it_begin / p.k_iters, kk = it_begin - tile * p.k_iters;
+    int m0 = (tile / p.n_tiles) * TM, nidx = tile % p.n_tiles;
+    const int first = min(S, it_end - it_begin);
+    for (int i = 0; i < first; ++i) {
+      if (elect_one()) issue_acts(i, m0, kk);
+      __syncwarp();
+      if (++kk == p.k_iters) {
+        kk = 0;
+        if (++nidx == p.n_tiles) { nidx = 0; m0 += TM; }
+      }
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -339,6 +363,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
+    pdl_wait_prior_grid();   // C and the partial-tile scratch may still be in use by the previous kernel
     int seg = 0;
     for (int it = it_begin; it < it_end; ++seg) {
       const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
@@ -433,7 +458,10 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       if (!warp_wait(smem_u32(&bars->empty[st]), ((pro_step / S) & 1) ^ 1, abort, p.wait_ns)) { give_up(p, abort, 5); break; }
       const long long c1 = W4A16_CLK();
       c_wait += c1 - c0;
-      if (elect_one()) issue_stage(st, pro_nidx, pro_m0, pro_kk);
+      if (elect_one()) {
+        issue_weights(st, pro_nidx, pro_kk);
+        issue_acts(st, pro_m0, pro_kk);
+      }
       __syncwarp();
       if (++pro_kk == p.k_iters) {
         pro_kk = 0;

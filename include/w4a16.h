@@ -44,6 +44,10 @@ extern "C" {
  * Enqueues on `stream` and returns; 0 at once when m, n or k is 0 (marlin_cute_kernel.cu:59-60).
  * Scratch beyond the caller's workspace (fp32 partial tiles of the stream-K fix-up) is owned by the
  * library and cached per (device, stream); its first use on a (device, stream) calls cudaMalloc.
+ * Stream order holds for A, C, workspace and the scratch.  B and s are treated as parameters: when the
+ * previous kernel on `stream` is another GEMM of this library, this one may prefetch B and s while that
+ * one is still finishing (programmatic dependent launch), so B and s must not be that GEMM's output.
+ * W4A16_PDL=0 in the environment restores plain stream order for everything.
  */
 int w4a16_marlin_gemm(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n, int prob_k,
                       void *workspace, int groupsize, int dev, void *stream, int thread_k, int thread_n, int sms,
