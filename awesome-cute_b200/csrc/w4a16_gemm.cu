@@ -211,7 +211,7 @@ int launch_tc(const Problem &pr) {
     p.partials = pr.fixed_partials;
     p.status = pr.fixed_status;
   } else {
-    StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 128 * w4a16::TILE_N);
+    StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 192 * w4a16::TILE_N);
     if (!ctx) return W4A16_ERR_CUDA;
     p.partials = ctx->partials;
     p.status = ctx->status;
@@ -244,7 +244,11 @@ int dispatch_tc(const Problem &pr) {
   const bool k256 = (pr.k % 256) == 0, k128 = (pr.k % 128) == 0;
   if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
   if (pr.m <= 32) return k256 ? launch_tc_g<32, 256>(pr) : k128 ? launch_tc_g<32, 128>(pr) : launch_tc_g<32, 64>(pr);
-  if (pr.m <= 64) return k128 ? launch_tc_g<64, 128>(pr) : launch_tc_g<64, 64>(pr);
+  if (pr.m <= 64) return k256 ? launch_tc_g<64, 256>(pr) : k128 ? launch_tc_g<64, 128>(pr) : launch_tc_g<64, 64>(pr);
+  // 192-row tiles (the widest that keep two accumulators and two operand buffers in TMEM) run ~12 % faster per
+  // flop than 128-row tiles on B200: take them unless their row padding costs more than that
+  const long pad192 = (long)((pr.m + 191) / 192) * 192, pad128 = (long)((pr.m + 127) / 128) * 128;
+  if (k128 && pad192 * 100 <= pad128 * 113) return launch_tc_g<192, 128>(pr);
   return k128 ? launch_tc_g<128, 128>(pr) : launch_tc_g<128, 64>(pr);
 }
 

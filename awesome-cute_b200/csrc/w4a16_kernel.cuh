@@ -87,7 +87,7 @@ struct Params {
 // 100+ clocks whatever its size, so bytes per TMA instruction is what bounds the load rate.
 template <int TM, int KS>
 struct Config {
-  static_assert(TM == 16 || TM == 32 || TM == 64 || TM == 128, "batch tile");
+  static_assert(TM == 16 || TM == 32 || TM == 64 || TM == 128 || TM == 192, "batch tile");
   static_assert(KS == 64 || KS == 128 || KS == 256, "k per stage");
   static constexpr int KCHUNKS = KS / 64;                    // 64-k swizzle atoms per stage
   static constexpr int GROUPS = KS >= 128 ? KS / 128 : 1;    // group-scale rows per stage

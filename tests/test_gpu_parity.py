@@ -89,6 +89,13 @@ def test_stream_k_split_counts(sms):
     run_problem(200, 512, 1024, groupsize=128, seed=sms, sms=sms)
 
 
+@pytest.mark.parametrize("m", [129, 192, 200, 384, 577, 2048])
+def test_wide_batch_tiles(m):
+    """Batches past 128 rows: the launcher picks 128- or 192-row tiles by padding; ragged last tiles."""
+    run_problem(m, 512, 1024, groupsize=128, seed=m)
+    run_problem(m, 256, 512, 64, 256, groupsize=-1, seed=m + 1)
+
+
 @pytest.mark.parametrize("m", [16, 128])
 def test_stream_k_large_k(m):
     """Skinny-m / large-k config: N=8192, K=28672 (oracle on a column window to stay in seconds)."""
