@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the W4A16 kernel uses: mbarrier, TMA
-// (cp.async.bulk.tensor, never with cluster multicast), tcgen05 (TMEM alloc, st/ld, mma, commit)
+// (cp.async.bulk.tensor, always to this CTA only), tcgen05 (TMEM alloc, st/ld, mma, commit)
 // and the slot accesses of the stream-K fix-up.
 //
 // Every wait in here is BOUNDED: it polls, and once a wall-clock limit has passed (or another

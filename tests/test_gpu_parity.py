@@ -231,3 +231,72 @@ def test_bounded_wait_runs_out_and_the_stream_survives():
     assert 0.25 < time.time() - t0 < 3.0          # it waited for the limit, not for ever
     assert _lib.lib.w4a16_device_status(0, stream) == _lib.OK      # status is cleared once read
     check(run_mul(At, Bt, st, m, n), orc.c_gemm(A, q, s, gs), "after the timeout")
+
+
+def test_dependent_chain_eager_and_graph_replay():
+    """Consecutive GEMMs on one stream where each one's output is the next one's activations: the next kernel
+    may start early (programmatic dependent launch) but must not read its activations, write C or touch the
+    scratch before the previous kernel has finished.  Checked eagerly and over several CUDA-graph replays."""
+    m, dims, gs = 16, [1024, 2048, 1024, 512], 128
+    rng = np.random.default_rng(91)
+    A0 = (rng.standard_normal((m, dims[0]), dtype=np.float32) * 0.5).astype(np.float16)
+    layers = []
+    for i in range(len(dims) - 1):
+        k, n = dims[i], dims[i + 1]
+        _, q, s = orc.make_problem(1, n, k, gs, 200 + i)
+        layers.append((q, s, to_dev(pkg.pack_weights(q)), to_dev(pkg.permute_scales(s)),
+                       torch.zeros(n // 128 * 16, dtype=torch.int, device=DEV)))
+    acts = [to_dev(A0)] + [torch.zeros((m, n), dtype=torch.half, device=DEV) for n in dims[1:]]
+
+    def chain():
+        for i, (q, s, Bt, st, ws) in enumerate(layers):
+            pkg.mul(acts[i], Bt, acts[i + 1], st, ws)
+
+    def verify(tag):
+        pkg.device_status(0)
+        for i, (q, s, Bt, st, ws) in enumerate(layers):
+            # each link against the oracle fed with the DEVICE's own input of that link
+            check(acts[i + 1], orc.c_gemm(acts[i].cpu().numpy(), q, s, gs), "%s link %d" % (tag, i))
+
+    for rep in range(3):
+        for a in acts[1:]:
+            a.zero_()
+        chain()
+        verify("eager %d" % rep)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        chain()
+    side.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        chain()
+        chain()
+    for rep in range(4):
+        for a in acts[1:]:
+            a.zero_()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        verify("graph %d" % rep)
+
+
+def test_random_shapes_stress():
+    """Many small random problems back to back on one stream (different tilings, split counts and scratch
+    reuse patterns), each checked against the oracle."""
+    rng = np.random.default_rng(123)
+    outs = []
+    for i in range(40):
+        m = int(rng.choice([1, 5, 16, 17, 33, 64, 100, 129, 200]))
+        n = 256 * int(rng.integers(1, 9))
+        k = 128 * int(rng.integers(1, 25))
+        gs = int(rng.choice([128, -1]))
+        sms = int(rng.choice([-1, -1, 148, 37, 11]))
+        A, q, s = orc.make_problem(m, n, k, gs, 1000 + i)
+        At, Bt, st = pack_problem(A, q, s)
+        C = torch.zeros((m, n), dtype=torch.half, device=DEV)
+        ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=DEV)
+        pkg.mul(At, Bt, C, st, ws, -1, -1, sms)
+        outs.append((C, A, q, s, gs, (m, n, k, gs, sms)))
+    pkg.device_status(0)
+    for (C, A, q, s, gs, tag) in outs:
+        check(C, orc.c_gemm(A, q, s, gs), str(tag))
