@@ -43,9 +43,9 @@ M_DECODE = 16
 COPIES = 3
 METRIC = "w4a16_weight_hbm_gbs_m16"
 UNIT = "GB/s"
-# DRAM bytes per launch from one ncu capture of each of the step's four kernels (mean of 26.14, 9.30, 46.68 and
-# 23.74 MB); the capture command and the per-shape figures are in profiles/decode_m16_dram_traffic.md.
-NCU_DRAM_BYTES_PER_LAUNCH = 26.47e6
+# DRAM bytes per launch from one ncu capture of each of the step's four kernels (mean of 26.16, 9.21, 46.68 and
+# 23.76 MB); the capture command and the per-shape figures are in profiles/decode_m16_dram_traffic.md.
+NCU_DRAM_BYTES_PER_LAUNCH = 26.45e6
 WORKLOAD = "llama2-7b linears (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)}, M=16, g128"
 
 
@@ -450,6 +450,100 @@ def run_case(args):
                       "weight_gbs": n * k / 2 / (med * 1e-6) / 1e9, "tflops": 2.0 * m * n * k / (med * 1e-6) / 1e12}), flush=True)
 
 
+def run_sharded70b(args):
+    """BASELINE.json configs[4]: Llama-2-70B layers column-sharded over the ranks (strong scaling: the layer is
+    fixed, each rank owns N/G columns), M in {16, 4096}, with and without the NCCL all-gather of the fp16 outputs.
+    One JSON line; `value` is the aggregate TFLOP/s at M = 4096 without the gather."""
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    gen = torch.Generator(device=dev).manual_seed(99 + rank)
+    layers70 = [("gate_up", 57344, 8192), ("down", 8192, 28672)]
+    side = torch.cuda.Stream(device=dev)
+    out = {}
+    for name, n_full, k in layers70:
+        n = n_full // world
+        copies = 2 if n * k // 2 > 70e6 else 4
+        Bs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen) for _ in range(copies)]
+        ss = [(torch.rand((k // GROUP, n), device=dev, generator=gen) * 0.015 + 0.005).half() for _ in range(copies)]
+        ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=dev)
+        for m in (16, 4096):
+            A = torch.randn((m, k), device=dev, generator=gen).half()
+            C = torch.zeros((m, n), dtype=torch.half, device=dev)
+            reps = 20 if m == 16 else 4
+
+            def one(i):
+                pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
+            with torch.cuda.stream(side):
+                one(0)
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(reps):
+                    one(i)
+            g.replay()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / reps
+            gms = None
+            if world > 1:
+                t = torch.tensor([ms], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+                for _ in range(2):
+                    one(0)
+                    full = pkg.all_gather_columns(C, world)
+                torch.cuda.synchronize()
+                dist.barrier()
+                a.record()
+                for i in range(reps):
+                    one(i)
+                    full = pkg.all_gather_columns(C, world)
+                b.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([a.elapsed_time(b) / reps], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                gms = float(t.item())
+                del full
+            flops = 2.0 * m * n_full * k
+            wb = n_full * k / 2
+            res = {"us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12, "weight_gbs": wb / (ms * 1e-3) / 1e9,
+                   "frac_hbm_per_gpu": wb / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                   "frac_tensor_per_gpu": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+            if gms is not None:
+                res["gathered_us"] = gms * 1e3
+                res["gathered_tflops"] = flops / (gms * 1e-3) / 1e12
+            out["%s_m%d" % (name, m)] = res
+            del A, C
+        del Bs, ss
+        torch.cuda.empty_cache()
+    pkg.device_status(local)
+    if rank == 0:
+        tf = sum(2.0 * 4096 * nf * k for _, nf, k in layers70) / sum(out["%s_m4096" % nm]["us"] * 1e-6 for nm, _, _ in layers70) / 1e12
+        print(json.dumps({"metric": "w4a16_llama70b_sharded_tflops_m4096", "value": tf, "unit": "TFLOP/s", "n_gpus": world,
+                          "higher_is_better": True, "scaling": "strong", "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": "llama2-70b gate-up 57344x8192 and down 8192x28672, column-sharded, g128, M in {16,4096}"},
+                          "results": out, "peaks": peaks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -459,8 +553,12 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the decode sweep and prefill extras")
     ap.add_argument("--case", default=None, help="NxKxM[xG]: time one shape only (graph replay; --eager for profilers)")
     ap.add_argument("--eager", action="store_true", help="with --case: plain launches instead of a CUDA graph")
+    ap.add_argument("--workload", default="decode7b", choices=["decode7b", "sharded70b"],
+                    help="decode7b: the headline step; sharded70b: Llama-2-70B layers column-sharded over the ranks")
     args = ap.parse_args()
-    if args.case:
+    if args.workload == "sharded70b":
+        run_sharded70b(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)
