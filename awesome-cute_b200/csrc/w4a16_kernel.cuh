@@ -6,7 +6,7 @@
 //
 // Formulation.  The problem is run transposed, D[n, m] = sum_k W[n, k] * A[m, k], so that
 //   * the 128 weight columns of a tile are the 128 rows (TMEM lanes) of a tcgen05.mma with M = 128,
-//   * the batch tile (TM = 16 .. 128 rows of A) is the UMMA N dimension, read K-major straight from
+//   * the batch tile (TM = 16 .. 192 rows of A) is the UMMA N dimension, read K-major straight from
 //     the shared-memory tile TMA wrote (128-byte swizzle),
 //   * the dequantised weights are the UMMA *A* operand and live in TENSOR MEMORY: each dequant thread
 //     owns one weight column, turns its packed nibbles into fp16 pairs in registers and writes them
