@@ -18,6 +18,7 @@
 #include "../../include/marlin_cute.h"
 #include "../../include/w4a16.h"
 #include "w4a16_kernel.cuh"
+#include "w4a16_kernel_2sm.cuh"
 
 namespace {
 
@@ -234,6 +235,107 @@ int launch_tc(const Problem &pr) {
   return W4A16_OK;
 }
 
+// ---- large batches on CTA pairs (cta_group::2): see w4a16_kernel_2sm.cuh
+template <int TM, bool GROUPED>
+int launch_tc2(const Problem &pr) {
+  using Cfg = w4a16::Config2<TM>;
+  auto kern = w4a16::w4a16_tc2_kernel<TM, GROUPED>;
+  constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
+  static bool attr_done[64] = {false};
+  static int max_pairs[64] = {0};
+
+  const int nsm = sm_count(pr.dev);
+  if (nsm <= 0) return W4A16_ERR_CUDA;
+
+  w4a16::Params p{};
+  p.m = pr.m, p.n = pr.n, p.k = pr.k;
+  p.n_tiles = pr.n / (2 * w4a16::TILE_N);            // 256-column tiles of the pair
+  p.m_tiles = (pr.m + TM - 1) / TM;
+  p.k_iters = pr.k / Cfg::KS;
+  const long total = (long)p.n_tiles * p.m_tiles * p.k_iters;
+  if (total > 0x7fffffffL) return W4A16_ERR_ARG;
+  p.total_iters = (int)total;
+  p.s = static_cast<const __half *>(pr.s);
+  p.C = static_cast<__half *>(pr.C);
+  p.wait_ns = pr.wait_ns;
+  p.a_box3d = 1;
+
+  CUtensorMap tmB, tmA, tmS;
+  {
+    const cuuint64_t dims[3] = {32, (cuuint64_t)(2 * pr.n / 32), (cuuint64_t)(pr.k / 16)};
+    const cuuint64_t strides[2] = {128, (cuuint64_t)pr.n * 8};
+    const cuuint32_t box[3] = {32, 8, (cuuint32_t)(Cfg::KS / 16)};
+    if (!encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, pr.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B"))
+      return W4A16_ERR_CUDA;
+  }
+  {  // each CTA of the pair loads half of the tile's rows
+    const cuuint64_t dims3[3] = {64, (cuuint64_t)pr.m, (cuuint64_t)(pr.k / 64)};
+    const cuuint64_t strides3[2] = {(cuuint64_t)pr.k * 2, 128};
+    const cuuint32_t box3[3] = {64, (cuuint32_t)Cfg::HALF_ROWS, (cuuint32_t)Cfg::KCHUNKS};
+    if (!encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pr.A, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B, "A3"))
+      return W4A16_ERR_CUDA;
+  }
+  if (GROUPED) {
+    const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
+    const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, 1};
+    if (!encode(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
+      return W4A16_ERR_CUDA;
+  } else {
+    tmS = tmA;
+  }
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3((unsigned)Cfg::THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = pr.stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!attr_done[pr.dev]) {
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"))
+      return W4A16_ERR_CUDA;
+    // the finisher of a split tile needs its contributors co-resident: never launch more pairs than fit at once
+    cfg.gridDim = dim3((unsigned)(nsm & ~1));
+    int clusters = 0;
+    if (!cuda_ok(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg), "cudaOccupancyMaxActiveClusters")) return W4A16_ERR_CUDA;
+    if (clusters < 1) {
+      g_last_error = "no CTA pair of the large-batch kernel fits on this device";
+      return W4A16_ERR_CUDA;
+    }
+    max_pairs[pr.dev] = clusters;
+    attr_done[pr.dev] = true;
+  }
+  int pairs = pr.sms > 0 ? pr.sms / 2 : nsm / 2;
+  if (pairs < 1) pairs = 1;
+  if (pairs > max_pairs[pr.dev]) pairs = max_pairs[pr.dev];
+  if (pairs > MAX_GRID / 2) pairs = MAX_GRID / 2;
+  if (pairs > p.total_iters) pairs = p.total_iters;
+  p.iters_per_cta = (p.total_iters + pairs - 1) / pairs;     // per PAIR
+  pairs = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 192 * w4a16::TILE_N);
+  if (!ctx) return W4A16_ERR_CUDA;
+  p.partials = ctx->partials;
+  p.status = ctx->status;
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, tmB, tmA, tmS, p), "kernel launch (CTA pairs)")) return W4A16_ERR_CUDA;
+  return W4A16_OK;
+}
+
+// W4A16_PAIRS=0 in the environment keeps large batches on the single-CTA kernel (debugging aid)
+const bool g_use_pairs = [] {
+  const char *e = std::getenv("W4A16_PAIRS");
+  return !(e && e[0] == '0');
+}();
+
 template <int TM, int KS>
 int launch_tc_g(const Problem &pr) {
   return pr.groupsize == 128 ? launch_tc<TM, KS, true>(pr) : launch_tc<TM, KS, false>(pr);
@@ -245,9 +347,17 @@ int dispatch_tc(const Problem &pr) {
   if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
   if (pr.m <= 32) return k256 ? launch_tc_g<32, 256>(pr) : k128 ? launch_tc_g<32, 128>(pr) : launch_tc_g<32, 64>(pr);
   if (pr.m <= 64) return k256 ? launch_tc_g<64, 256>(pr) : k128 ? launch_tc_g<64, 128>(pr) : launch_tc_g<64, 64>(pr);
-  // 192-row tiles (the widest that keep two accumulators and two operand buffers in TMEM) run ~12 % faster per
-  // flop than 128-row tiles on B200: take them unless their row padding costs more than that
+  // batches past 64 rows: 128- or 192-row tiles (192 is the widest that keeps two accumulators and two operand
+  // buffers in TMEM)
   const long pad192 = (long)((pr.m + 191) / 192) * 192, pad128 = (long)((pr.m + 127) / 128) * 128;
+  // Large batches run on CTA pairs (two SMs per 256-column tile, half the activation traffic per SM): +16 % to +43 %
+  // over the single-CTA kernel on B200.  192-row tiles beat 128-row tiles by ~8 % there, 12 % on the single-CTA
+  // kernel: take them unless their row padding costs more than that.
+  if (g_use_pairs && k128 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
+    if (pad192 * 100 <= pad128 * 106)
+      return pr.groupsize == 128 ? launch_tc2<192, true>(pr) : launch_tc2<192, false>(pr);
+    return pr.groupsize == 128 ? launch_tc2<128, true>(pr) : launch_tc2<128, false>(pr);
+  }
   if (k128 && pad192 * 100 <= pad128 * 113) return launch_tc_g<192, 128>(pr);
   return k128 ? launch_tc_g<128, 128>(pr) : launch_tc_g<128, 64>(pr);
 }
