@@ -307,13 +307,10 @@ int launch_tc2(const Problem &pr) {
     cfg.gridDim = dim3((unsigned)(nsm & ~1));
     int clusters = 0;
     if (!cuda_ok(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg), "cudaOccupancyMaxActiveClusters")) return W4A16_ERR_CUDA;
-    if (clusters < 1) {
-      g_last_error = "no CTA pair of the large-batch kernel fits on this device";
-      return W4A16_ERR_CUDA;
-    }
     max_pairs[pr.dev] = clusters;
     attr_done[pr.dev] = true;
   }
+  if (max_pairs[pr.dev] < 1) return -2;   // no CTA pair can be scheduled here: the caller takes the single-CTA kernel
   int pairs = pr.sms > 0 ? pr.sms / 2 : nsm / 2;
   if (pairs < 1) pairs = 1;
   if (pairs > max_pairs[pr.dev]) pairs = max_pairs[pr.dev];
@@ -354,9 +351,12 @@ int dispatch_tc(const Problem &pr) {
   // over the single-CTA kernel on B200.  192-row tiles beat 128-row tiles by ~8 % there, 12 % on the single-CTA
   // kernel: take them unless their row padding costs more than that.
   if (g_use_pairs && k128 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
+    int rc;
     if (pad192 * 100 <= pad128 * 106)
-      return pr.groupsize == 128 ? launch_tc2<192, true>(pr) : launch_tc2<192, false>(pr);
-    return pr.groupsize == 128 ? launch_tc2<128, true>(pr) : launch_tc2<128, false>(pr);
+      rc = pr.groupsize == 128 ? launch_tc2<192, true>(pr) : launch_tc2<192, false>(pr);
+    else
+      rc = pr.groupsize == 128 ? launch_tc2<128, true>(pr) : launch_tc2<128, false>(pr);
+    if (rc != -2) return rc;
   }
   if (k128 && pad192 * 100 <= pad128 * 113) return launch_tc_g<192, 128>(pr);
   return k128 ? launch_tc_g<128, 128>(pr) : launch_tc_g<128, 64>(pr);

@@ -233,11 +233,12 @@ def test_bounded_wait_runs_out_and_the_stream_survives():
     check(run_mul(At, Bt, st, m, n), orc.c_gemm(A, q, s, gs), "after the timeout")
 
 
-def test_dependent_chain_eager_and_graph_replay():
+@pytest.mark.parametrize("m", [16, 256])
+def test_dependent_chain_eager_and_graph_replay(m):
     """Consecutive GEMMs on one stream where each one's output is the next one's activations: the next kernel
     may start early (programmatic dependent launch) but must not read its activations, write C or touch the
     scratch before the previous kernel has finished.  Checked eagerly and over several CUDA-graph replays."""
-    m, dims, gs = 16, [1024, 2048, 1024, 512], 128
+    dims, gs = [1024, 2048, 1024, 512], 128
     rng = np.random.default_rng(91)
     A0 = (rng.standard_normal((m, dims[0]), dtype=np.float32) * 0.5).astype(np.float16)
     layers = []
@@ -300,3 +301,29 @@ def test_random_shapes_stress():
     pkg.device_status(0)
     for (C, A, q, s, gs, tag) in outs:
         check(C, orc.c_gemm(A, q, s, gs), str(tag))
+
+
+def test_single_cta_kernels_for_large_batches():
+    """W4A16_PAIRS=0 keeps large batches on the single-CTA kernel (128- and 192-row tiles); checked in a child
+    process because the switch is read once at load time."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys, os; sys.path.insert(0, os.getcwd()); sys.path.insert(0, os.path.join(os.getcwd(), 'tests'))\n"
+        "from gpu_common import run_problem\n"
+        "for m in (129, 192, 400, 1024):\n"
+        "    run_problem(m, 512, 1024, groupsize=128, seed=m)\n"
+        "    run_problem(m, 256, 512, 64, 256, groupsize=-1, seed=m + 1, sms=9)\n"
+        "print('ok')\n")
+    env = dict(os.environ, W4A16_PAIRS="0")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("sms", [2, 3, 9, 40, 147, 148])
+def test_cta_pair_split_counts(sms):
+    """The large-batch kernel with every way of cutting 256-column tiles between CTA pairs (sms / 2 pairs)."""
+    run_problem(300, 1024, 2048, groupsize=128, seed=sms, sms=sms)
+    run_problem(1000, 512, 1024, 64, 256, groupsize=-1, seed=sms + 7, sms=sms)
