@@ -236,10 +236,10 @@ int launch_tc(const Problem &pr) {
 }
 
 // ---- large batches on CTA pairs (cta_group::2): see w4a16_kernel_2sm.cuh
-template <int TM, bool GROUPED>
+template <int TM, int KS, bool GROUPED>
 int launch_tc2(const Problem &pr) {
-  using Cfg = w4a16::Config2<TM>;
-  auto kern = w4a16::w4a16_tc2_kernel<TM, GROUPED>;
+  using Cfg = w4a16::Config2<TM, KS>;
+  auto kern = w4a16::w4a16_tc2_kernel<TM, KS, GROUPED>;
   constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
   static bool attr_done[64] = {false};
   static int max_pairs[64] = {0};
@@ -278,7 +278,7 @@ int launch_tc2(const Problem &pr) {
   if (GROUPED) {
     const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
     const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, 1};
+    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, (cuuint32_t)Cfg::GROUPS};
     if (!encode(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
       return W4A16_ERR_CUDA;
   } else {
@@ -343,6 +343,11 @@ int dispatch_tc(const Problem &pr) {
   const bool k256 = (pr.k % 256) == 0, k128 = (pr.k % 128) == 0;
   if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
   if (pr.m <= 32) return k256 ? launch_tc_g<32, 256>(pr) : k128 ? launch_tc_g<32, 128>(pr) : launch_tc_g<32, 64>(pr);
+  // 33..64 rows: the activation tile is already twice the weight bytes of a stage; a CTA pair halves it (+8-12 %)
+  if (g_use_pairs && pr.m > 32 && pr.m <= 64 && k256 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
+    const int rc = pr.groupsize == 128 ? launch_tc2<64, 256, true>(pr) : launch_tc2<64, 256, false>(pr);
+    if (rc != -2) return rc;
+  }
   if (pr.m <= 64) return k256 ? launch_tc_g<64, 256>(pr) : k128 ? launch_tc_g<64, 128>(pr) : launch_tc_g<64, 64>(pr);
   // batches past 64 rows: 128- or 192-row tiles (192 is the widest that keeps two accumulators and two operand
   // buffers in TMEM)
@@ -353,9 +358,9 @@ int dispatch_tc(const Problem &pr) {
   if (g_use_pairs && k128 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
     int rc;
     if (pad192 * 100 <= pad128 * 106)
-      rc = pr.groupsize == 128 ? launch_tc2<192, true>(pr) : launch_tc2<192, false>(pr);
+      rc = pr.groupsize == 128 ? launch_tc2<192, 128, true>(pr) : launch_tc2<192, 128, false>(pr);
     else
-      rc = pr.groupsize == 128 ? launch_tc2<128, true>(pr) : launch_tc2<128, false>(pr);
+      rc = pr.groupsize == 128 ? launch_tc2<128, 128, true>(pr) : launch_tc2<128, 128, false>(pr);
     if (rc != -2) return rc;
   }
   if (k128 && pad192 * 100 <= pad128 * 113) return launch_tc_g<192, 128>(pr);

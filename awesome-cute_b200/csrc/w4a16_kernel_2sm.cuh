@@ -19,15 +19,17 @@
 
 namespace w4a16 {
 
-template <int TM>
+template <int TM, int KS_ = 128>
 struct Config2 {
-  static_assert(TM == 128 || TM == 192, "batch tile of the pair");
-  static constexpr int KS = 128;
-  static constexpr int KCHUNKS = 2;
+  static_assert(TM == 64 || TM == 128 || TM == 192, "batch tile of the pair");
+  static_assert(KS_ == 128 || KS_ == 256, "k per stage");
+  static constexpr int KS = KS_;
+  static constexpr int KCHUNKS = KS / 64;
+  static constexpr int GROUPS = KS / 128;
   static constexpr int HALF_ROWS = TM / 2;                   // activation rows held by each CTA
-  static constexpr int W_BYTES = KS * TILE_N / 2;            // 8 KB
-  static constexpr int A_BYTES = HALF_ROWS * KS * 2;         // [2 chunks][TM/2 rows][128 B]
-  static constexpr int S_BYTES = TILE_N * 2;
+  static constexpr int W_BYTES = KS * TILE_N / 2;            // 8 or 16 KB
+  static constexpr int A_BYTES = HALF_ROWS * KS * 2;         // [KS/64 chunks][TM/2 rows][128 B]
+  static constexpr int S_BYTES = GROUPS * TILE_N * 2;
   static constexpr int STAGE_BYTES = W_BYTES + A_BYTES + S_BYTES;
   static constexpr int ACC_STRIDE = TM;
   static constexpr int WBUF_COL0 = 2 * ACC_STRIDE;
@@ -60,11 +62,11 @@ struct Bars2 {  // same offsets in both CTAs of the pair
 };
 static_assert(sizeof(Bars2) <= 1024, "barrier block");
 
-template <int TM, bool GROUPED>
-__global__ void __launch_bounds__(Config2<TM>::THREADS, 1)
+template <int TM, int KS_, bool GROUPED>
+__global__ void __launch_bounds__(Config2<TM, KS_>::THREADS, 1)
 w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                  const __grid_constant__ CUtensorMap tmS, const Params p) {
-  using Cfg = Config2<TM>;
+  using Cfg = Config2<TM, KS_>;
   using namespace sm100;
   constexpr int S = Cfg::STAGES, NDQ = Cfg::NDQ, KS = Cfg::KS;
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;
@@ -93,7 +95,7 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     const int n_idx = 2 * n_idx2 + (int)rank;
     mbar_expect_tx(full, WS_TX);
     tma_load_3d(smem_u32(sW) + st * Cfg::W_BYTES, &tmB, 0, n_idx * 8, kk * (KS / 16), full);
-    if (GROUPED) tma_load_2d(smem_u32(sS) + st * Cfg::S_BYTES, &tmS, n_idx * TILE_N, kk, full);
+    if (GROUPED) tma_load_2d(smem_u32(sS) + st * Cfg::S_BYTES, &tmS, n_idx * TILE_N, kk * Cfg::GROUPS, full);
   };
   auto issue_acts = [&](int st, int m0, int kk) {          // this CTA's half of the activation rows
     const uint32_t leader_full = map_to_cta(smem_u32(&bars->afull[st]), 0);
@@ -154,14 +156,14 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
       d_full += c1 - c0;
       const uint32_t wbase = sW_u + st * Cfg::W_BYTES;
       __half2 sc = *reinterpret_cast<const __half2 *>(&one2);
-      if (GROUPED) {
-        uint16_t sv;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sS_u + st * Cfg::S_BYTES + s_off));
-        sc = __half2half2(__ushort_as_half(sv));
-      }
       bool buf_ok = true;
 #pragma unroll
       for (int half = 0; half < Cfg::KCHUNKS; ++half) {
+        if (GROUPED && (half & 1) == 0) {   // a new 128-k group starts every second 64-k chunk
+          uint16_t sv;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(sS_u + st * Cfg::S_BYTES + (half >> 1) * (TILE_N * 2) + s_off));
+          sc = __half2half2(__ushort_as_half(sv));
+        }
         uint32_t v[32];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
