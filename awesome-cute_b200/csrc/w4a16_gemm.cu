@@ -342,6 +342,11 @@ int dispatch_tc(const Problem &pr) {
   // batch tile = UMMA N; the k per stage is as deep as the activation tile allows (fewer, larger TMAs)
   const bool k256 = (pr.k % 256) == 0, k128 = (pr.k % 128) == 0;
   if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
+  // 17..32 rows on CTA pairs as well (+12-16 %)
+  if (g_use_pairs && pr.m > 16 && pr.m <= 32 && k256 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
+    const int rc = pr.groupsize == 128 ? launch_tc2<32, 256, true>(pr) : launch_tc2<32, 256, false>(pr);
+    if (rc != -2) return rc;
+  }
   if (pr.m <= 32) return k256 ? launch_tc_g<32, 256>(pr) : k128 ? launch_tc_g<32, 128>(pr) : launch_tc_g<32, 64>(pr);
   // 33..64 rows: the activation tile is already twice the weight bytes of a stage; a CTA pair halves it (+8-12 %)
   if (g_use_pairs && pr.m > 32 && pr.m <= 64 && k256 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {

@@ -21,7 +21,7 @@ namespace w4a16 {
 
 template <int TM, int KS_ = 128>
 struct Config2 {
-  static_assert(TM == 64 || TM == 128 || TM == 192, "batch tile of the pair");
+  static_assert(TM == 32 || TM == 64 || TM == 128 || TM == 192, "batch tile of the pair");
   static_assert(KS_ == 128 || KS_ == 256, "k per stage");
   static constexpr int KS = KS_;
   static constexpr int KCHUNKS = KS / 64;
