@@ -360,9 +360,13 @@ int dispatch_tc(const Problem &pr) {
   // Large batches run on CTA pairs (two SMs per 256-column tile, half the activation traffic per SM): +16 % to +43 %
   // over the single-CTA kernel on B200.  192-row tiles beat 128-row tiles by ~8 % there, 12 % on the single-CTA
   // kernel: take them unless their row padding costs more than that.
-  if (g_use_pairs && k128 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
+  // ... when each pair gets at least ~32 k-stages: on smaller problems the single-CTA kernel's shorter start-up and
+  // fix-up win (4096 x 4096 at m = 128: 17.5 us against 25.7 us)
+  const long tm = pad192 * 100 <= pad128 * 106 ? 192 : 128;
+  const long pair_stages = (long)(pr.n / 256) * ((pr.m + tm - 1) / tm) * (pr.k / 128) / 74;
+  if (g_use_pairs && k128 && pr.n % 256 == 0 && pair_stages >= 32 && !pr.fixed_partials && !pr.orphan_finisher) {
     int rc;
-    if (pad192 * 100 <= pad128 * 106)
+    if (tm == 192)
       rc = pr.groupsize == 128 ? launch_tc2<192, 128, true>(pr) : launch_tc2<192, 128, false>(pr);
     else
       rc = pr.groupsize == 128 ? launch_tc2<128, 128, true>(pr) : launch_tc2<128, 128, false>(pr);

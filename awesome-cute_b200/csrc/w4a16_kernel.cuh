@@ -171,6 +171,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
   using namespace sm100;
   constexpr int S = Cfg::STAGES;
   constexpr int NDQ = Cfg::NDQ;
+  constexpr bool HELP = TM >= 64;   // dequant warps help to finish a split tile (see the epilogue)
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;
   constexpr uint32_t STAGE_TX = Cfg::W_BYTES + Cfg::A_BYTES + (GROUPED ? Cfg::S_BYTES : 0);
 
@@ -356,6 +357,77 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       W4A16_STAMP(4);                               // last dequant of set 0
       W4A16_BUCKET(4, d_full); W4A16_BUCKET(5, d_wempty); W4A16_BUCKET(6, d_work);
     }
+    if (HELP) {
+      // ---- help to finish the CTA's last tile if it is a split one (chunks 16*(1+set), +48, ... of this quadrant)
+      int seg = 0, l_tile = 0, l_kb = 1, l_ke = 0, l_seg = 0;
+      for (int it = it_begin; it < it_end; ++seg) {
+        l_tile = it / p.k_iters;
+        l_kb = it - l_tile * p.k_iters;
+        l_ke = min(p.k_iters, l_kb + (it_end - it));
+        l_seg = seg;
+        it += l_ke - l_kb;
+      }
+      if (it_end > it_begin && l_kb == 0 && l_ke < p.k_iters) {
+        const int n0 = (l_tile % p.n_tiles) * TILE_N, m0 = (l_tile / p.n_tiles) * TM;
+        const int acc = l_seg & 1;
+        const int last_contrib = ((l_tile + 1) * p.k_iters - 1) / p.iters_per_cta;
+        __half sch = __float2half(1.0f);
+        if (!GROUPED) {
+          const int c32 = row & 31;
+          sch = p.s[n0 + row - c32 + 8 * ((c32 & 7) >> 1) + 2 * (c32 >> 3) + (c32 & 1)];
+        }
+        pdl_wait_prior_grid();
+        bool ok = warp_wait(smem_u32(&bars->accfull[acc]), (l_seg >> 1) & 1, abort, p.wait_ns);
+        tc_fence_after();
+        const uint64_t t0 = globaltimer_ns();
+        const uint32_t t_acc = tmem + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_STRIDE;
+#pragma unroll 1
+        for (int c0 = 16 * (1 + set); c0 < TM && ok; c0 += 48) {
+          uint32_t v[16];
+          tmem_ld_32x32b_x16(t_acc + c0, v);
+          tc_wait_ld();
+          for (int c = (int)blockIdx.x + 1; c <= last_contrib && ok; c += 2) {
+            uint32_t *src[2];
+#pragma unroll
+            for (int f = 0; f < 2; ++f) src[f] = p.partials + ((size_t)min(c + f, last_contrib) * TM + c0) * TILE_N + row;
+            uint32_t x[2][16];
+            for (uint32_t spin = 0;; ++spin) {
+              bool up = true;
+#pragma unroll
+              for (int f = 0; f < 2; ++f)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) x[f][i] = ld_slot(src[f] + (size_t)i * TILE_N);
+#pragma unroll
+              for (int f = 0; f < 2; ++f)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
+              if (__all_sync(0xffffffffu, up)) break;
+              if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > p.wait_ns)) { ok = false; break; }
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int f = 0; f < 2; ++f) {
+              if (c + f <= last_contrib) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(x[f][i]));
+                  st_slot(src[f] + (size_t)i * TILE_N, PARTIAL_IDLE);
+                }
+              }
+            }
+          }
+          if (!ok) break;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int mm = m0 + c0 + i;
+            __half h = __float2half(__uint_as_float(v[i]));
+            if (!GROUPED) h = __hmul(h, sch);
+            if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+          }
+        }
+        if (!ok) give_up(p, abort, 9);
+      }
+    }
   } else if (warp < NDQ + EPI_WARPS) {
     // =========================================================== epilogue warps
     // Each warp serves its own TMEM lane quadrant = 32 weight columns, end to end (its partial-tile slots
@@ -386,8 +458,11 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       bool ok = true;
       const uint64_t t0 = ncontrib > 0 ? globaltimer_ns() : 0ull;
       constexpr int FLY = TM <= 32 ? 4 : 2;   // contributors whose slices are in flight together
+      // A split tile of 64+ rows is the last thing its finisher does, and folding the contributors' slices in is a
+      // chain of L2 round trips per 16 columns: the CTA's dequant warps, idle by now, take two thirds of the chunks.
+      const int c_step = (HELP && finisher && ncontrib > 0) ? 48 : 16;
 #pragma unroll 1
-      for (int c0 = 0; c0 < TM && ok; c0 += 16) {
+      for (int c0 = 0; c0 < TM && ok; c0 += c_step) {
         uint32_t v[16];
         tmem_ld_32x32b_x16(t_lane + acc * Cfg::ACC_STRIDE + c0, v);
         tc_wait_ld();
