@@ -30,6 +30,10 @@ SYMBOLS = {
     "w4a16_unpermute_scales": (_i, [_vp, _i, _i, _vp]),
     "w4a16_quantize_pack": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "w4a16_shard_columns": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
+    "w4a16_quantize_pack_device": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "w4a16_blob_write": (_i, [ctypes.c_char_p, _vp, _vp, _i, _i, _i]),
+    "w4a16_blob_info": (_i, [ctypes.c_char_p, ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
+    "w4a16_blob_read": (_i, [ctypes.c_char_p, _i, _i, _vp, _vp]),
 }
 
 

@@ -223,3 +223,51 @@ class Layer(nn.Module):
         B, sp = quantize_pack(w, s, gs)
         self.B[:, :] = torch.from_numpy(B).to(self.B.device)
         self.s[:, :] = torch.from_numpy(sp).to(self.s.device)
+
+
+# ----------------------------------------------------------------------------- device-side pack, files
+def quantize_pack_device(weight_nk, scales, groupsize):
+    """Layer.pack on the device: weight fp16 [n, k] (CUDA), scales fp16 [groups, n] (CUDA) -> (B int32 [k/16, 2n],
+    s_packed fp16 [groups, n]) on the same device.  Bit-exact with quantize_pack()."""
+    if not (weight_nk.is_cuda and scales.is_cuda):
+        raise RuntimeError("quantize_pack_device() needs CUDA tensors")
+    if weight_nk.dtype != torch.half or scales.dtype != torch.half:
+        raise ValueError('Only `torch.half` weights and scales are supported.')
+    weight_nk, scales = weight_nk.contiguous(), scales.contiguous()
+    n, k = weight_nk.shape
+    groups = 1 if groupsize == -1 else k // groupsize
+    B = torch.empty((k // 16, 2 * n), dtype=torch.int, device=weight_nk.device)
+    sp = torch.empty((groups, n), dtype=torch.half, device=weight_nk.device)
+    dev = weight_nk.get_device()
+    with torch.cuda.device(dev):
+        err = _L.w4a16_quantize_pack_device(weight_nk.data_ptr(), scales.data_ptr(), k, n, groupsize, B.data_ptr(),
+                                            sp.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    if err:
+        raise ValueError("w4a16_quantize_pack_device: code %d" % err)
+    return B, sp
+
+
+def save_packed(path, B, s_packed):
+    """Write a packed layer (numpy B int32 [k/16, 2n], s_packed fp16 [groups, n]) to a file."""
+    B, sp = _np(B, np.int32), _np(s_packed, np.float16)
+    k, n = B.shape[0] * 16, B.shape[1] // 2
+    groupsize = -1 if sp.shape[0] == 1 else k // sp.shape[0]
+    err = _L.w4a16_blob_write(str(path).encode(), _vp(B), _vp(sp), k, n, groupsize)
+    if err:
+        raise ValueError("w4a16_blob_write: code %d" % err)
+
+
+def load_packed(path, rank=0, world=1):
+    """Read a packed layer, or column shard `rank` of `world` of it, from a file -> (B, s_packed, groupsize)."""
+    k, n, gs, groups = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    err = _L.w4a16_blob_info(str(path).encode(), ctypes.byref(k), ctypes.byref(n), ctypes.byref(gs), ctypes.byref(groups))
+    if err:
+        raise ValueError("w4a16_blob_info: code %d" % err)
+    if world < 1 or n.value % world:
+        raise ValueError("n=%d does not split over %d ranks" % (n.value, world))
+    B = np.empty((k.value // 16, 2 * n.value // world), np.int32)
+    sp = np.empty((groups.value, n.value // world), np.float16)
+    err = _L.w4a16_blob_read(str(path).encode(), rank, world, _vp(B), _vp(sp))
+    if err:
+        raise ValueError("w4a16_blob_read: code %d" % err)
+    return B, sp, gs.value

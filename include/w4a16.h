@@ -144,6 +144,19 @@ int w4a16_quantize_pack(const uint16_t *weight_nk, const uint16_t *scales, int k
 int w4a16_shard_columns(const int32_t *B, const uint16_t *s_packed, int k, int n, int groups, int rank, int world,
                         int32_t *B_shard, uint16_t *s_shard);
 
+/* Layer.pack on the DEVICE (gemm/marlin_gemm/marlin.py:92-131 runs it with numpy on the host): weight fp16 [n, k]
+ * and scales fp16 [k/groupsize or 1, n] in device memory -> B int32 [k/16, 2n] and s_packed in device memory,
+ * enqueued on `stream`.  Bit-exact with w4a16_quantize_pack. */
+int w4a16_quantize_pack_device(const void *weight_nk, const void *scales, int k, int n, int groupsize, void *B,
+                               void *s_packed, void *stream);
+
+/* ---- packed layers on disk (host pointers).  The reference keeps packed layers only as torch buffers
+ * (gemm/marlin_gemm/marlin.py:82-83); these give them a file form: 64-byte header, B, s.  Reading takes column
+ * shard `rank` of `world` straight from the file (1, 0 reads the whole layer). */
+int w4a16_blob_write(const char *path, const int32_t *B, const uint16_t *s_packed, int k, int n, int groupsize);
+int w4a16_blob_info(const char *path, int *k, int *n, int *groupsize, int *groups);
+int w4a16_blob_read(const char *path, int rank, int world, int32_t *B_shard, uint16_t *s_shard);
+
 #ifdef __cplusplus
 }
 #endif

@@ -327,3 +327,23 @@ def test_cta_pair_split_counts(sms):
     """The large-batch kernel with every way of cutting 256-column tiles between CTA pairs (sms / 2 pairs)."""
     run_problem(300, 1024, 2048, groupsize=128, seed=sms, sms=sms)
     run_problem(1000, 512, 1024, 64, 256, groupsize=-1, seed=sms + 7, sms=sms)
+
+
+@pytest.mark.parametrize("groupsize", [128, -1])
+def test_device_quantize_pack_is_bit_exact(groupsize):
+    """Layer.pack on the device against the host packer (itself pinned to the reference packer's golden vectors),
+    on raw fp16 weights (every rounding case of round(w / s), clamping included), then through the GEMM."""
+    k, n, m = 512, 1024, 16
+    rng = np.random.default_rng(61)
+    w = (rng.standard_normal((n, k), dtype=np.float32) * 0.06).astype(np.float16)       # [n, k] like nn.Linear.weight
+    groups = 1 if groupsize == -1 else k // groupsize
+    s = rng.uniform(0.005, 0.02, size=(groups, n)).astype(np.float16)
+    B_host, sp_host = pkg.quantize_pack(w, s, groupsize)
+    B_dev, sp_dev = pkg.quantize_pack_device(to_dev(w), to_dev(s), groupsize)
+    torch.cuda.synchronize()
+    assert np.array_equal(B_dev.cpu().numpy(), B_host)
+    assert np.array_equal(sp_dev.cpu().numpy().view(np.uint16), sp_host.view(np.uint16))
+    A = rng.standard_normal((m, k), dtype=np.float32).astype(np.float16)
+    C = run_mul(to_dev(A), B_dev, sp_dev, m, n)
+    q = orc.np_quantize(np.ascontiguousarray(w.T), s, groupsize)
+    check(C, orc.c_gemm(A, q, s, groupsize), "device-packed")

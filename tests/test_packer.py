@@ -87,3 +87,36 @@ def test_shard_rejects_ragged():
     sp = np.zeros((1, 384), np.float16)
     with pytest.raises(ValueError):
         pkg.shard_columns(B, sp, 0, 2)   # 192 columns per rank is not a multiple of 128
+
+
+def test_blob_roundtrip_and_shard_on_load(tmp_path):
+    k, n = 256, 1024
+    rng = np.random.default_rng(8)
+    q = rng.integers(0, 16, size=(k, n), dtype=np.uint8)
+    s = rng.uniform(0.005, 0.02, size=(k // 128, n)).astype(np.float16)
+    B, sp = pkg.pack_weights(q), pkg.permute_scales(s)
+    path = tmp_path / "layer.w4a16"
+    pkg.save_packed(path, B, sp)
+    assert path.stat().st_size == 64 + B.nbytes + sp.nbytes
+    B2, sp2, gs = pkg.load_packed(path)
+    assert gs == 128 and np.array_equal(B2, B) and np.array_equal(sp2.view(np.uint16), sp.view(np.uint16))
+    for world in (2, 4):
+        for r in range(world):
+            Bs, ss, _ = pkg.load_packed(path, r, world)
+            want_B, want_s = pkg.shard_columns(B, sp, r, world)
+            assert np.array_equal(Bs, want_B) and np.array_equal(ss.view(np.uint16), want_s.view(np.uint16))
+    with pytest.raises(ValueError):
+        pkg.load_packed(path, 0, 16)            # 64 columns per rank: not a multiple of 128
+    # per-channel layer
+    s1 = rng.uniform(0.005, 0.02, size=(1, n)).astype(np.float16)
+    pkg.save_packed(path, B, pkg.permute_scales(s1))
+    assert pkg.load_packed(path)[2] == -1
+
+
+def test_blob_rejects_foreign_files(tmp_path):
+    path = tmp_path / "junk.bin"
+    path.write_bytes(b"not a packed layer" * 10)
+    with pytest.raises(ValueError):
+        pkg.load_packed(path)
+    with pytest.raises(ValueError):
+        pkg.load_packed(tmp_path / "missing.w4a16")
