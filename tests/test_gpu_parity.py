@@ -347,3 +347,51 @@ def test_device_quantize_pack_is_bit_exact(groupsize):
     C = run_mul(to_dev(A), B_dev, sp_dev, m, n)
     q = orc.np_quantize(np.ascontiguousarray(w.T), s, groupsize)
     check(C, orc.c_gemm(A, q, s, groupsize), "device-packed")
+
+
+def test_pair_kernel_dependent_chain_graph_replay():
+    """Two large-batch GEMMs (CTA-pair kernel) where the first one's output is the second one's activations,
+    eagerly and over CUDA-graph replays; the oracle is evaluated on column windows, fed with the device's own
+    activations of each link."""
+    m, gs = 1024, 128
+    dims = [4096, 8192, 4096]
+    rng = np.random.default_rng(17)
+    A0 = (rng.standard_normal((m, dims[0]), dtype=np.float32) * 0.25).astype(np.float16)
+    layers = []
+    for i in range(2):
+        k, n = dims[i], dims[i + 1]
+        q = rng.integers(0, 16, size=(k, n), dtype=np.uint8)
+        s = rng.uniform(0.005, 0.02, size=(k // gs, n)).astype(np.float16)
+        layers.append((q, s, to_dev(pkg.pack_weights(q)), to_dev(pkg.permute_scales(s)),
+                       torch.zeros(n // 128 * 16, dtype=torch.int, device=DEV)))
+    acts = [to_dev(A0)] + [torch.zeros((m, n), dtype=torch.half, device=DEV) for n in dims[1:]]
+
+    def chain():
+        for i, (q, s, Bt, st, ws) in enumerate(layers):
+            pkg.mul(acts[i], Bt, acts[i + 1], st, ws)
+
+    def verify(tag):
+        pkg.device_status(0)
+        for i, (q, s, Bt, st, ws) in enumerate(layers):
+            a_in = acts[i].cpu().numpy()
+            for n0 in (0, dims[i + 1] - 256):
+                ref = orc.c_gemm(a_in, np.ascontiguousarray(q[:, n0:n0 + 256]), np.ascontiguousarray(s[:, n0:n0 + 256]), gs)
+                check(acts[i + 1][:, n0:n0 + 256], ref, "%s link %d window %d" % (tag, i, n0))
+
+    chain()
+    verify("eager")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        chain()
+    side.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        chain()
+        chain()
+    for rep in range(2):
+        for a in acts[1:]:
+            a.zero_()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        verify("graph %d" % rep)
