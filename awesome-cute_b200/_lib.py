@@ -34,6 +34,12 @@ SYMBOLS = {
     "w4a16_blob_write": (_i, [ctypes.c_char_p, _vp, _vp, _i, _i, _i]),
     "w4a16_blob_info": (_i, [ctypes.c_char_p, ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "w4a16_blob_read": (_i, [ctypes.c_char_p, _i, _i, _vp, _vp]),
+    "w4a16_marlin_gemm_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, ctypes.POINTER(_vp), _i, _i]),
+    "w4a16_peer_alloc": (_i, [ctypes.c_size_t, ctypes.POINTER(_vp), _vp]),
+    "w4a16_peer_open": (_i, [_vp, ctypes.POINTER(_vp)]),
+    "w4a16_peer_close": (_i, [_vp]),
+    "w4a16_peer_free": (_i, [_vp]),
+    "w4a16_peer_barrier": (_i, [ctypes.POINTER(_vp), _i, _i, _i, _vp, _i]),
 }
 
 

@@ -10,6 +10,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <string>
@@ -126,7 +127,19 @@ struct Problem {
   // set only by the bounded-wait self-test: launch CTA 0 alone, so that it waits for partial tiles nobody writes
   bool orphan_finisher = false;
   uint64_t wait_ns = w4a16::WAIT_LIMIT_NS;
+  // set only by the gathering entry point: C is [m][c_ld], this GEMM's columns start at c_col0, and every finished
+  // tile also goes to the same place of n_extra further buffers
+  int c_ld = 0, c_col0 = 0, n_extra = 0;
+  void *C_extra[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
+
+void set_output(w4a16::Params &p, const Problem &pr) {
+  p.C = static_cast<__half *>(pr.C);
+  p.c_ld = pr.c_ld > 0 ? pr.c_ld : pr.n;
+  p.c_col0 = pr.c_col0;
+  p.n_extra = pr.n_extra;
+  for (int d = 0; d < 7; ++d) p.C_extra[d] = static_cast<__half *>(pr.C_extra[d]);
+}
 
 template <int TM, int KS, bool GROUPED>
 int launch_tc(const Problem &pr) {
@@ -154,7 +167,7 @@ int launch_tc(const Problem &pr) {
   p.iters_per_cta = (p.total_iters + grid - 1) / grid;
   grid = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
   p.s = static_cast<const __half *>(pr.s);
-  p.C = static_cast<__half *>(pr.C);
+  set_output(p, pr);
   p.wait_ns = pr.wait_ns;
   if (pr.orphan_finisher) {
     if (p.k_iters < 2) return W4A16_ERR_ARG;
@@ -256,7 +269,7 @@ int launch_tc2(const Problem &pr) {
   if (total > 0x7fffffffL) return W4A16_ERR_ARG;
   p.total_iters = (int)total;
   p.s = static_cast<const __half *>(pr.s);
-  p.C = static_cast<__half *>(pr.C);
+  set_output(p, pr);
   p.wait_ns = pr.wait_ns;
   p.a_box3d = 1;
 
@@ -643,6 +656,125 @@ extern "C" int w4a16_device_status(int dev, void *stream) {
 }
 
 extern "C" const char *w4a16_last_cuda_error(void) { return g_last_error.c_str(); }
+
+// ---------------------------------------------------------------------------------------------------------
+// Column-sharded GEMM with a gathering epilogue, and the peer-memory plumbing it needs.  One process per GPU.
+
+extern "C" int w4a16_marlin_gemm_gather(const void *A, const void *B, const void *s, int prob_m, int n_local, int prob_k,
+                                        void *workspace, int groupsize, int dev, void *stream, void *const *dst,
+                                        int world, int rank) {
+  (void)workspace;
+  if (prob_m < 0 || n_local < 0 || prob_k < 0) return W4A16_ERR_ARG;
+  if (!dst || world < 1 || world > 8 || rank < 0 || rank >= world) {
+    g_last_error = "gather: world must be 1..8 and 0 <= rank < world";
+    return W4A16_ERR_ARG;
+  }
+  int thread_k = -1, thread_n = -1;
+  const int chk = check_problem(prob_m, n_local, prob_k, groupsize, thread_k, thread_n);
+  if (chk == -1) return W4A16_OK;
+  if (chk != W4A16_OK) return chk;
+  if (!A || !B || !s) return W4A16_ERR_ARG;
+  uintptr_t bits = reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(s);
+  for (int r = 0; r < world; ++r) {
+    if (!dst[r]) return W4A16_ERR_ARG;
+    bits |= reinterpret_cast<uintptr_t>(dst[r]);
+  }
+  if (bits & 15) return W4A16_ERR_ARG;
+  if (dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  if ((long)n_local * world > 0x7fffffffL) return W4A16_ERR_ARG;
+  Problem pr{A, B, s, dst[rank], prob_m, n_local, prob_k, groupsize, dev, -1, static_cast<cudaStream_t>(stream)};
+  pr.c_ld = n_local * world;
+  pr.c_col0 = n_local * rank;
+  for (int r = 0; r < world; ++r)
+    if (r != rank) pr.C_extra[pr.n_extra++] = dst[r];
+  return dispatch_tc(pr);
+}
+
+extern "C" int w4a16_peer_alloc(size_t bytes, void **dptr, void *handle64) {
+  if (!dptr || !handle64 || bytes == 0) return W4A16_ERR_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+  void *p = nullptr;
+  if (!cuda_ok(cudaMalloc(&p, bytes), "cudaMalloc(peer buffer)")) return W4A16_ERR_CUDA;
+  cudaIpcMemHandle_t h;
+  if (!cuda_ok(cudaMemset(p, 0, bytes), "cudaMemset(peer buffer)") ||
+      !cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize") ||
+      !cuda_ok(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle")) {
+    cudaFree(p);
+    return W4A16_ERR_CUDA;
+  }
+  std::memcpy(handle64, &h, sizeof(h));
+  *dptr = p;
+  return W4A16_OK;
+}
+
+extern "C" int w4a16_peer_open(const void *handle64, void **dptr) {
+  if (!dptr || !handle64) return W4A16_ERR_ARG;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  void *p = nullptr;
+  if (!cuda_ok(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) return W4A16_ERR_CUDA;
+  *dptr = p;
+  return W4A16_OK;
+}
+
+extern "C" int w4a16_peer_close(void *dptr) {
+  return cuda_ok(cudaIpcCloseMemHandle(dptr), "cudaIpcCloseMemHandle") ? W4A16_OK : W4A16_ERR_CUDA;
+}
+
+extern "C" int w4a16_peer_free(void *dptr) { return cuda_ok(cudaFree(dptr), "cudaFree") ? W4A16_OK : W4A16_ERR_CUDA; }
+
+namespace {
+struct PeerFlags {
+  uint32_t *p[8];
+};
+
+// One warp.  Flag block of a rank: words 0..7 = the epoch last announced by rank r, word 8 = this rank's own epoch
+// counter.  The epoch lives on the device, so a captured launch keeps working when it is replayed.
+__global__ void peer_barrier_kernel(PeerFlags f, int world, int rank, uint64_t wait_ns, int *status) {
+  const int lane = threadIdx.x;
+  uint32_t *mine = f.p[rank];
+  uint32_t e = 0;
+  if (lane == 0) {
+    e = mine[8] + 1;
+    mine[8] = e;
+  }
+  e = __shfl_sync(0xffffffffu, e, 0);
+  __threadfence_system();
+  if (lane < world) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.p[lane] + rank), "r"(e) : "memory");
+    const uint64_t t0 = sm100::globaltimer_ns();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + lane) : "memory");
+      if ((int32_t)(v - e) >= 0) break;
+      if (sm100::globaltimer_ns() - t0 > wait_ns) {
+        atomicCAS(status, 0, w4a16::STATUS_TIMEOUT | (30 << 8));
+        break;
+      }
+    }
+  }
+}
+}  // namespace
+
+extern "C" int w4a16_peer_barrier(void *const *flags, int world, int rank, int dev, void *stream, int limit_ms) {
+  if (!flags || world < 1 || world > 8 || rank < 0 || rank >= world || dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  if (limit_ms < 1 || limit_ms > 5000) return W4A16_ERR_ARG;
+  PeerFlags f{};
+  for (int r = 0; r < world; ++r) {
+    if (!flags[r] || (reinterpret_cast<uintptr_t>(flags[r]) & 63)) return W4A16_ERR_ARG;
+    f.p[r] = static_cast<uint32_t *>(flags[r]);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int *status = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    StreamCtx *ctx = get_ctx(dev, st, (size_t)MAX_GRID * 192 * w4a16::TILE_N);
+    if (!ctx) return W4A16_ERR_CUDA;
+    status = ctx->status;
+  }
+  peer_barrier_kernel<<<1, 32, 0, st>>>(f, world, rank, (uint64_t)limit_ms * 1000000ull, status);
+  return cuda_ok(cudaGetLastError(), "barrier launch") ? W4A16_OK : W4A16_ERR_CUDA;
+}
 
 #ifdef W4A16_TRACE
 // trace builds only: point the kernels at a [gridDim.x][16] uint64 buffer for phase time stamps

@@ -76,11 +76,22 @@ struct Params {
   int total_iters, iters_per_cta;
   int a_box3d;                          // 1: tmA is the 3-D view (one box per stage), 0: 2-D (one box per 64 k)
   const __half *s;                      // scales (read directly by the epilogue when per-channel)
-  __half *C;
+  __half *C;                            // fp16 [m][c_ld]; this GEMM's columns start at c_col0
+  int c_ld, c_col0;                     // plain GEMM: c_ld = n, c_col0 = 0
+  int n_extra;                          // further destinations that receive the same tile (gathering epilogue), 0..7
+  __half *C_extra[7];                   // same shape as C; may be peer-mapped memory of other GPUs (plain stores only)
   uint32_t *partials;                   // [gridDim.x][TM][128] fp32 partial tiles; PARTIAL_IDLE between launches
   int *status;                          // 0, or STATUS_TIMEOUT | (site << 8)
   uint64_t wait_ns;                     // every device-side wait gives up after this long (WAIT_LIMIT_NS by default)
 };
+
+// One finished output element to C and, in the gathering form, to every further destination (plain 2-byte stores,
+// 64 contiguous bytes per warp and row; a peer GPU's memory is only ever written, never read, by this library).
+__device__ __forceinline__ void store_c(const Params &p, int mm, int col, __half h) {
+  const size_t off = (size_t)mm * p.c_ld + p.c_col0 + col;
+  p.C[off] = h;
+  for (int d = 0; d < p.n_extra; ++d) p.C_extra[d][off] = h;
+}
 
 // Tile configuration.  TM = batch tile (UMMA N); KS = k per pipeline stage.  The stage is the unit of
 // every hand-off; it is made large (256 k for small TM) because issuing a TMA costs the producer
@@ -422,7 +433,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
             const int mm = m0 + c0 + i;
             __half h = __float2half(__uint_as_float(v[i]));
             if (!GROUPED) h = __hmul(h, sch);
-            if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+            if (mm < p.m) store_c(p, mm, n0 + row, h);
           }
         }
         if (!ok) give_up(p, abort, 9);
@@ -510,7 +521,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
             const int mm = m0 + c0 + i;
             __half h = __float2half(__uint_as_float(v[i]));
             if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
-            if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+            if (mm < p.m) store_c(p, mm, n0 + row, h);
           }
         }
       }

@@ -261,7 +261,7 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
             const int mm = m0 + c0 + i;
             __half h = __float2half(__uint_as_float(v[i]));
             if (!GROUPED) h = __hmul(h, sch);
-            if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+            if (mm < p.m) store_c(p, mm, n0 + row, h);
           }
         }
         if (!ok) give_up(p, abort, 19);
@@ -341,7 +341,7 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
             const int mm = m0 + c0 + i;
             __half h = __float2half(__uint_as_float(v[i]));
             if (!GROUPED) h = __hmul(h, sch);
-            if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+            if (mm < p.m) store_c(p, mm, n0 + row, h);
           }
         }
       }

@@ -90,6 +90,25 @@ def mul_host(A_host, B, C_host, s, workspace, A_stage, C_stage):
         _check(err, prob_m, prob_n, prob_k, -1, -1, groupsize)
 
 
+def mul_gather(A, B, s, workspace, dst_ptrs, rank):
+    """Column-shard GEMM whose epilogue writes this rank's columns into every rank's [m, world * n_local] buffer
+    (w4a16_marlin_gemm_gather).  dst_ptrs: device addresses of the `world` destination buffers as seen from this
+    process (own buffer at index `rank`, peer-mapped ones elsewhere).  No counterpart in the reference."""
+    prob_m, prob_k = A.shape
+    n_local = B.shape[1] // 2
+    groupsize = -1 if s.shape[0] == 1 else prob_k // s.shape[0]
+    world = len(dst_ptrs)
+    dev = A.get_device()
+    if torch.cuda.current_device() != dev:
+        raise RuntimeError("device %d must be current" % dev)
+    arr = (ctypes.c_void_p * world)(*[int(p) for p in dst_ptrs])
+    err = _L.w4a16_marlin_gemm_gather(A.data_ptr(), B.data_ptr(), s.data_ptr(), prob_m, n_local, prob_k,
+                                      workspace.data_ptr(), groupsize, dev, torch.cuda.current_stream(dev).cuda_stream,
+                                      arr, world, rank)
+    if err:
+        _check(err, prob_m, n_local, prob_k, -1, -1, groupsize)
+
+
 def mul_simt(A, B, C, s, workspace, thread_k=-1, thread_n=-1, sms=-1, max_par=16):
     """Same call through the diagnostic CUDA-core kernel (tests only)."""
     mul(A, B, C, s, workspace, thread_k, thread_n, sms, max_par, _entry=_L.w4a16_marlin_gemm_simt)

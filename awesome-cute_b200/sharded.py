@@ -4,13 +4,20 @@ The reference is single-GPU; this is the only multi-GPU piece.  A column shard i
 packed operands (both Marlin permutations are local to 64-column blocks, gemm/marlin_gemm/marlin.py:29-57),
 so every rank runs the unchanged GEMM on its slice and there is no reduction between GPUs.  The one
 exchange step, used only when the caller asks for the full output row, is an all-gather of the fp16
-outputs along N (NCCL over NVLink on GPUs, gloo in the CPU tests).
+outputs along N.  Two forms: a plain all-gather (NCCL over NVLink on GPUs, gloo in the CPU tests), and the
+gathering epilogue, where the GEMM kernel itself stores every finished tile into all ranks' output buffers
+over peer-mapped memory (`GatherBuffers`, `ColumnShardedLayer.forward_gathered`), followed by a one-warp
+barrier kernel instead of a collective.
 """
+import ctypes
+
 import numpy as np
 import torch
 import torch.distributed as dist
 
-from . import marlin
+from . import _lib, marlin
+
+_L = _lib.lib
 
 
 class ColumnShardedLayer:
@@ -46,6 +53,85 @@ class ColumnShardedLayer:
         if not gather:
             return C
         return all_gather_columns(C, self.world, group)
+
+    def forward_gathered(self, A, bufs, barrier=True):
+        """Full [m, n] output on every rank without a collective: the GEMM's epilogue stores this rank's columns
+        into every rank's buffer of `bufs` (a GatherBuffers), then the barrier kernel orders the ranks.  The
+        returned tensor is a view of bufs.local; it is overwritten by the next call with the same `bufs`, which
+        must not be issued before every rank has consumed this result (barrier, or alternate two GatherBuffers)."""
+        m = A.shape[0]
+        if m > bufs.m_max or bufs.n != self.n or bufs.world != self.world:
+            raise ValueError("GatherBuffers do not fit this layer / batch")
+        marlin.mul_gather(A, self.B, self.s, self.workspace, bufs.dst_ptrs, self.rank)
+        if barrier:
+            bufs.barrier()
+        return bufs.local[:m]
+
+
+class _RawDeviceArray:
+    """Lets torch view device memory that this library allocated (CUDA array interface, version 2)."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 2, "strides": None}
+
+
+class GatherBuffers:
+    """One fp16 [m_max, n] output buffer per rank, each mapped into every other rank's process, plus the flag
+    blocks of the barrier.  Collective over `group` (handles travel by all_gather_object); the rank's device must
+    be current.  `local` is this rank's buffer as a torch tensor; after `barrier()` it holds all ranks' columns."""
+
+    def __init__(self, m_max, n, rank, world, device, group=None):
+        self.rank, self.world, self.m_max, self.n = rank, world, m_max, n
+        self.device = torch.device(device)
+        self.dev = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        data_bytes = (m_max * n * 2 + 255) // 256 * 256
+        self._bytes = data_bytes + 64
+        base = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        self._check(_L.w4a16_peer_alloc(self._bytes, ctypes.byref(base), handle), "w4a16_peer_alloc")
+        self._own = base.value
+        self._opened = []
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, handle.raw, group=group)
+        bases = []
+        for r in range(world):
+            if r == rank:
+                bases.append(self._own)
+                continue
+            p = ctypes.c_void_p()
+            self._check(_L.w4a16_peer_open(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(p)),
+                        "w4a16_peer_open")
+            self._opened.append(p.value)
+            bases.append(p.value)
+        self.dst_ptrs = bases
+        self._flags = (ctypes.c_void_p * world)(*[b + data_bytes for b in bases])
+        self.local = torch.as_tensor(_RawDeviceArray(self._own, (m_max, n), "<f2"), device=self.device)
+
+    @staticmethod
+    def _check(err, what):
+        if err:
+            raise RuntimeError("%s failed with code %d: %s" % (what, err, _lib.last_cuda_error()))
+
+    def barrier(self, limit_ms=2000):
+        """Enqueue the cross-GPU barrier on the current stream (w4a16_peer_barrier)."""
+        self._check(_L.w4a16_peer_barrier(self._flags, self.world, self.rank, self.dev,
+                                          torch.cuda.current_stream(self.dev).cuda_stream, limit_ms),
+                    "w4a16_peer_barrier")
+
+    def close(self, group=None):
+        """Unmap the peers' buffers, then (after every rank has unmapped) free the own one."""
+        torch.cuda.synchronize(self.dev)
+        for p in self._opened:
+            _L.w4a16_peer_close(p)
+        self._opened = []
+        if self.world > 1:
+            dist.barrier(group=group)
+        if self._own:
+            self.local = None
+            _L.w4a16_peer_free(self._own)
+            self._own = None
 
 
 def all_gather_columns(C_local, world, group=None):

@@ -10,6 +10,7 @@
 #ifndef W4A16_H_
 #define W4A16_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -94,6 +95,42 @@ int w4a16_marlin_gemm_builtin_scratch(const void *A, const void *B, void *C, con
 int w4a16_marlin_gemm_host(const void *A_host, const void *B, void *C_host, const void *s, int prob_m, int prob_n,
                            int prob_k, void *workspace, int groupsize, int dev, void *stream, void *A_stage,
                            void *C_stage);
+
+/* ---- column-sharded GEMM with a gathering epilogue (one process per GPU).  The reference is single-GPU and has
+ * no counterpart; the shard rule follows from its layout (gemm/marlin_gemm/marlin.py:29-57: both permutations stay
+ * inside 64-column blocks).
+ *
+ * Rank `rank` of `world` (<= 8) holds columns [rank*n_local, (rank+1)*n_local) of the layer (B, s as produced by
+ * w4a16_shard_columns).  dst[r] is an fp16 [m, world*n_local] row-major buffer in GPU r's memory, as addressable
+ * from THIS process: dst[rank] is local, the others come from w4a16_peer_open.  The kernel's epilogue writes every
+ * finished tile into its columns of ALL world buffers with plain stores (peer memory is never read and never the
+ * source of a TMA copy), so the transfer over NVLink overlaps the main loop tile by tile and no separate all-gather
+ * runs.  A rank may read the other ranks' columns of its own buffer only after w4a16_peer_barrier on the same
+ * stream, and must not start the next gathering GEMM into the same buffers before every rank has finished reading
+ * (barrier again, or alternate two sets of buffers).  Return codes as w4a16_marlin_gemm (n_local plays prob_n). */
+int w4a16_marlin_gemm_gather(const void *A, const void *B, const void *s, int prob_m, int n_local, int prob_k,
+                             void *workspace, int groupsize, int dev, void *stream, void *const *dst, int world,
+                             int rank);
+
+/* Device memory that other processes of this machine can map.  w4a16_peer_alloc: cudaMalloc on the current device,
+ * zero-filled, plus its 64-byte inter-process handle (pass it to the other ranks by any host channel).
+ * w4a16_peer_open: maps another process's buffer for the current device and enables peer access to its GPU
+ * (cudaIpcOpenMemHandle); never call it on a handle of the own process.  Close what was opened before the owner
+ * frees it. */
+int w4a16_peer_alloc(size_t bytes, void **dptr, void *handle64);
+int w4a16_peer_open(const void *handle64, void **dptr);
+int w4a16_peer_close(void *dptr);
+int w4a16_peer_free(void *dptr);
+
+/* Stream-ordered barrier over the ranks' GPUs: enqueues a one-warp kernel that announces this rank's next epoch in
+ * every rank's flag block and waits (at most limit_ms, 1..5000) until every rank has announced it here.  flags[r]
+ * = rank r's flag block: 64 bytes, 64-byte aligned, zero when first used (w4a16_peer_alloc zero-fills), mapped like
+ * dst above.  Work enqueued on `stream` before the call is complete and visible on all ranks when the barrier
+ * kernel of each rank ends.  The epoch counter lives in the flag block, so a captured barrier can be replayed.
+ * Every rank must run its barrier kernel on its own GPU; never two ranks on one GPU.  A wait that runs out is
+ * reported by w4a16_device_status(dev, stream) as W4A16_ERR_TIMEOUT; the flag blocks must then be zeroed again by
+ * all ranks before further use. */
+int w4a16_peer_barrier(void *const *flags, int world, int rank, int dev, void *stream, int limit_ms);
 
 /* Size rule of the caller's lock array: n / 128 * max_par  (gemm/marlin_gemm/marlin_gemm.cpp:29-31,
  * gemm/marlin_gemm/marlin.py:85). */

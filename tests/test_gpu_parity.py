@@ -395,3 +395,53 @@ def test_pair_kernel_dependent_chain_graph_replay():
         g.replay()
         torch.cuda.synchronize()
         verify("graph %d" % rep)
+
+
+@pytest.mark.parametrize("m,nl,k", [(16, 512, 1024), (48, 256, 2048), (200, 512, 512), (1024, 2048, 4096)])
+def test_gathering_epilogue_on_one_gpu(m, nl, k):
+    """The gathering GEMM with three destinations that all live on this GPU (the kernel only sees pointers): every
+    destination receives this rank's columns, bit-identical to the plain GEMM, and nothing else is touched."""
+    world, rank = 3, 1
+    An, q, sn = orc.make_problem(m, nl, k, 128, m + nl)
+    A, Bt, st = pack_problem(An, q, sn)
+    ref = orc.c_gemm(An, q, sn, 128)
+    ws = torch.zeros(nl // 128 * 16, dtype=torch.int, device=DEV)
+    C = torch.zeros((m, nl), dtype=torch.half, device=DEV)
+    pkg.mul(A, Bt, C, st, ws)
+    dst = [torch.full((m, world * nl), 7.0, dtype=torch.half, device=DEV) for _ in range(world)]
+    for _ in range(2):
+        pkg.mul_gather(A, Bt, st, ws, [d.data_ptr() for d in dst], rank)
+    pkg.device_status(0)
+    check(C, ref, "plain")
+    for d in dst:
+        assert torch.equal(d[:, rank * nl:(rank + 1) * nl], C)
+        assert bool((d[:, :rank * nl] == 7.0).all()) and bool((d[:, (rank + 1) * nl:] == 7.0).all())
+    assert int(ws.abs().sum()) == 0
+
+
+def test_gather_buffers_single_rank_and_barrier():
+    """GatherBuffers with a world of one (no peers to map): allocation, the torch view of the library's memory,
+    the barrier kernel (trivially satisfied) over several epochs, and release."""
+    m, n, k = 16, 512, 1024
+    An, q, sn = orc.make_problem(m, n, k, 128, 3)
+    layer = pkg.ColumnShardedLayer(pkg.pack_weights(q), pkg.permute_scales(sn), 0, 1, DEV)
+    bufs = pkg.GatherBuffers(32, n, 0, 1, DEV)
+    for _ in range(3):
+        out = layer.forward_gathered(to_dev(An), bufs)
+    pkg.device_status(0)
+    check(out, orc.c_gemm(An, q, sn, 128), "gathered world 1")
+    bufs.close()
+
+
+def test_peer_barrier_gives_up_when_a_rank_never_arrives():
+    """A barrier over two ranks of which only this one exists: the flag nothing sets makes the bounded wait run
+    out; the status says so and the stream stays usable."""
+    import ctypes
+    flags = torch.zeros(32, dtype=torch.int, device=DEV)    # two 64-byte flag blocks
+    arr = (ctypes.c_void_p * 2)(flags.data_ptr(), flags.data_ptr() + 64)
+    L = pkg._lib.lib
+    assert L.w4a16_peer_barrier(arr, 2, 0, 0, torch.cuda.current_stream().cuda_stream, 50) == 0
+    with pytest.raises(RuntimeError, match="timed out"):
+        pkg.device_status(0)
+    pkg.device_status(0)
+    test_gather_buffers_single_rank_and_barrier()
