@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <array>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -130,7 +131,7 @@ struct Problem {
   // set only by the gathering entry point: C is [m][c_ld], this GEMM's columns start at c_col0, and every finished
   // tile also goes to the same place of n_extra further buffers
   int c_ld = 0, c_col0 = 0, n_extra = 0;
-  void *C_extra[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  void *const *C_extra = nullptr;   // device table of the n_extra further buffers
 };
 
 void set_output(w4a16::Params &p, const Problem &pr) {
@@ -138,13 +139,13 @@ void set_output(w4a16::Params &p, const Problem &pr) {
   p.c_ld = pr.c_ld > 0 ? pr.c_ld : pr.n;
   p.c_col0 = pr.c_col0;
   p.n_extra = pr.n_extra;
-  for (int d = 0; d < 7; ++d) p.C_extra[d] = static_cast<__half *>(pr.C_extra[d]);
+  p.C_extra = reinterpret_cast<__half *const *>(pr.C_extra);
 }
 
-template <int TM, int KS, bool GROUPED>
+template <int TM, int KS, bool GROUPED, bool GATHER>
 int launch_tc(const Problem &pr) {
   using Cfg = w4a16::Config<TM, KS>;
-  auto kern = w4a16::w4a16_tc_kernel<TM, KS, GROUPED>;
+  auto kern = w4a16::w4a16_tc_kernel<TM, KS, GROUPED, GATHER>;
   // at least 116 KiB so that two CTAs can never share an SM (each one allocates all of TMEM)
   constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
   static bool attr_done[64] = {false};
@@ -249,10 +250,10 @@ int launch_tc(const Problem &pr) {
 }
 
 // ---- large batches on CTA pairs (cta_group::2): see w4a16_kernel_2sm.cuh
-template <int TM, int KS, bool GROUPED>
+template <int TM, int KS, bool GROUPED, bool GATHER>
 int launch_tc2(const Problem &pr) {
   using Cfg = w4a16::Config2<TM, KS>;
-  auto kern = w4a16::w4a16_tc2_kernel<TM, KS, GROUPED>;
+  auto kern = w4a16::w4a16_tc2_kernel<TM, KS, GROUPED, GATHER>;
   constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
   static bool attr_done[64] = {false};
   static int max_pairs[64] = {0};
@@ -346,9 +347,19 @@ const bool g_use_pairs = [] {
   return !(e && e[0] == '0');
 }();
 
+// the gathering epilogue is a separate instantiation, so the plain GEMM's code is untouched by it
 template <int TM, int KS>
 int launch_tc_g(const Problem &pr) {
-  return pr.groupsize == 128 ? launch_tc<TM, KS, true>(pr) : launch_tc<TM, KS, false>(pr);
+  if (pr.c_ld > 0)
+    return pr.groupsize == 128 ? launch_tc<TM, KS, true, true>(pr) : launch_tc<TM, KS, false, true>(pr);
+  return pr.groupsize == 128 ? launch_tc<TM, KS, true, false>(pr) : launch_tc<TM, KS, false, false>(pr);
+}
+
+template <int TM, int KS>
+int launch_tc2_g(const Problem &pr) {
+  if (pr.c_ld > 0)
+    return pr.groupsize == 128 ? launch_tc2<TM, KS, true, true>(pr) : launch_tc2<TM, KS, false, true>(pr);
+  return pr.groupsize == 128 ? launch_tc2<TM, KS, true, false>(pr) : launch_tc2<TM, KS, false, false>(pr);
 }
 
 int dispatch_tc(const Problem &pr) {
@@ -357,13 +368,13 @@ int dispatch_tc(const Problem &pr) {
   if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
   // 17..32 rows on CTA pairs as well (+12-16 %)
   if (g_use_pairs && pr.m > 16 && pr.m <= 32 && k256 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
-    const int rc = pr.groupsize == 128 ? launch_tc2<32, 256, true>(pr) : launch_tc2<32, 256, false>(pr);
+    const int rc = launch_tc2_g<32, 256>(pr);
     if (rc != -2) return rc;
   }
   if (pr.m <= 32) return k256 ? launch_tc_g<32, 256>(pr) : k128 ? launch_tc_g<32, 128>(pr) : launch_tc_g<32, 64>(pr);
   // 33..64 rows: the activation tile is already twice the weight bytes of a stage; a CTA pair halves it (+8-12 %)
   if (g_use_pairs && pr.m > 32 && pr.m <= 64 && k256 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
-    const int rc = pr.groupsize == 128 ? launch_tc2<64, 256, true>(pr) : launch_tc2<64, 256, false>(pr);
+    const int rc = launch_tc2_g<64, 256>(pr);
     if (rc != -2) return rc;
   }
   if (pr.m <= 64) return k256 ? launch_tc_g<64, 256>(pr) : k128 ? launch_tc_g<64, 128>(pr) : launch_tc_g<64, 64>(pr);
@@ -380,9 +391,9 @@ int dispatch_tc(const Problem &pr) {
   if (g_use_pairs && k128 && pr.n % 256 == 0 && pair_stages >= 32 && !pr.fixed_partials && !pr.orphan_finisher) {
     int rc;
     if (tm == 192)
-      rc = pr.groupsize == 128 ? launch_tc2<192, 128, true>(pr) : launch_tc2<192, 128, false>(pr);
+      rc = launch_tc2_g<192, 128>(pr);
     else
-      rc = pr.groupsize == 128 ? launch_tc2<128, 128, true>(pr) : launch_tc2<128, 128, false>(pr);
+      rc = launch_tc2_g<128, 128>(pr);
     if (rc != -2) return rc;
   }
   if (k128 && pad192 * 100 <= pad128 * 113) return launch_tc_g<192, 128>(pr);
@@ -660,6 +671,10 @@ extern "C" const char *w4a16_last_cuda_error(void) { return g_last_error.c_str()
 // ---------------------------------------------------------------------------------------------------------
 // Column-sharded GEMM with a gathering epilogue, and the peer-memory plumbing it needs.  One process per GPU.
 
+namespace {
+std::map<std::array<uintptr_t, 9>, void *> g_dst_tables;   // (device, up to 7 destinations, 0-padded) -> device table
+}
+
 extern "C" int w4a16_marlin_gemm_gather(const void *A, const void *B, const void *s, int prob_m, int n_local, int prob_k,
                                         void *workspace, int groupsize, int dev, void *stream, void *const *dst,
                                         int world, int rank) {
@@ -685,8 +700,24 @@ extern "C" int w4a16_marlin_gemm_gather(const void *A, const void *B, const void
   Problem pr{A, B, s, dst[rank], prob_m, n_local, prob_k, groupsize, dev, -1, static_cast<cudaStream_t>(stream)};
   pr.c_ld = n_local * world;
   pr.c_col0 = n_local * rank;
-  for (int r = 0; r < world; ++r)
-    if (r != rank) pr.C_extra[pr.n_extra++] = dst[r];
+  if (world > 1) {
+    // the other ranks' buffers, as a table in device memory that is made once per distinct set of destinations
+    std::array<uintptr_t, 9> key{};
+    key[0] = (uintptr_t)dev;
+    for (int r = 0; r < world; ++r)
+      if (r != rank) key[1 + pr.n_extra++] = reinterpret_cast<uintptr_t>(dst[r]);
+    std::lock_guard<std::mutex> lock(g_mu);
+    void *&tab = g_dst_tables[key];
+    if (!tab) {
+      if (!cuda_ok(cudaMalloc(&tab, 8 * sizeof(void *)), "cudaMalloc(destination table)")) return W4A16_ERR_CUDA;
+      if (!cuda_ok(cudaMemcpy(tab, &key[1], 8 * sizeof(void *), cudaMemcpyHostToDevice), "cudaMemcpy(destination table)")) {
+        cudaFree(tab);
+        g_dst_tables.erase(key);
+        return W4A16_ERR_CUDA;
+      }
+    }
+    pr.C_extra = static_cast<void *const *>(tab);
+  }
   return dispatch_tc(pr);
 }
 

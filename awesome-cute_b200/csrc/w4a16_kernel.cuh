@@ -76,21 +76,41 @@ struct Params {
   int total_iters, iters_per_cta;
   int a_box3d;                          // 1: tmA is the 3-D view (one box per stage), 0: 2-D (one box per 64 k)
   const __half *s;                      // scales (read directly by the epilogue when per-channel)
-  __half *C;                            // fp16 [m][c_ld]; this GEMM's columns start at c_col0
-  int c_ld, c_col0;                     // plain GEMM: c_ld = n, c_col0 = 0
-  int n_extra;                          // further destinations that receive the same tile (gathering epilogue), 0..7
-  __half *C_extra[7];                   // same shape as C; may be peer-mapped memory of other GPUs (plain stores only)
+  __half *C;
   uint32_t *partials;                   // [gridDim.x][TM][128] fp32 partial tiles; PARTIAL_IDLE between launches
   int *status;                          // 0, or STATUS_TIMEOUT | (site << 8)
   uint64_t wait_ns;                     // every device-side wait gives up after this long (WAIT_LIMIT_NS by default)
+  // gathering instantiations only: C is [m][c_ld], this GEMM's columns start at c_col0, and every finished tile also
+  // goes to n_extra (0..7) further buffers of that shape, which may be peer GPUs' memory (plain stores only).  Their
+  // addresses sit in a small table in device memory: with them inline, the kernel's parameters pass 512 bytes, and
+  // past that size ptxas was seen to spill registers in every instantiation, the plain GEMM's included.
+  int c_ld, c_col0, n_extra;
+  __half *const *C_extra;
 };
+static_assert(3 * sizeof(CUtensorMap) + sizeof(Params) <= 512, "keep the kernel parameters within 512 bytes");
 
-// One finished output element to C and, in the gathering form, to every further destination (plain 2-byte stores,
-// 64 contiguous bytes per warp and row; a peer GPU's memory is only ever written, never read, by this library).
-__device__ __forceinline__ void store_c(const Params &p, int mm, int col, __half h) {
-  const size_t off = (size_t)mm * p.c_ld + p.c_col0 + col;
-  p.C[off] = h;
-  for (int d = 0; d < p.n_extra; ++d) p.C_extra[d][off] = h;
+// Gathering epilogue: sixteen finished rows of one weight column (v: fp32 bit patterns) to C and to every further
+// destination (plain 2-byte stores, 64 contiguous bytes per warp and row; peer memory is only ever written).
+// Destinations are the outer loop, so that one pointer is live at a time.
+template <bool GROUPED>
+__device__ __forceinline__ void store_chunk_gather(const Params &p, const uint32_t (&v)[16], __half sch, int mrow0, int col) {
+  __half2 hv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    __half lo = __float2half(__uint_as_float(v[2 * i])), hi = __float2half(__uint_as_float(v[2 * i + 1]));
+    if (!GROUPED) lo = __hmul(lo, sch), hi = __hmul(hi, sch);  // after the fp16 convert, as in the plain epilogue
+    hv[i] = __halves2half2(lo, hi);
+  }
+  const size_t off0 = (size_t)mrow0 * p.c_ld + p.c_col0 + col;
+  const int rows = p.m - mrow0;   // rows of this chunk that exist (may exceed 16)
+  for (int d = 0; d <= p.n_extra; ++d) {
+    __half *dst = (d == 0 ? p.C : p.C_extra[d - 1]) + off0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (2 * i < rows) dst[(size_t)(2 * i) * p.c_ld] = __low2half(hv[i]);
+      if (2 * i + 1 < rows) dst[(size_t)(2 * i + 1) * p.c_ld] = __high2half(hv[i]);
+    }
+  }
 }
 
 // Tile configuration.  TM = batch tile (UMMA N); KS = k per pipeline stage.  The stage is the unit of
@@ -174,7 +194,7 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 scale, uint32_t
   hi = *reinterpret_cast<uint32_t *>(&b);
 }
 
-template <int TM, int KS, bool GROUPED>
+template <int TM, int KS, bool GROUPED, bool GATHER = false>
 __global__ void __launch_bounds__(Config<TM, KS>::THREADS, 1)
 w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                 const __grid_constant__ CUtensorMap tmS, const Params p) {
@@ -428,12 +448,16 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
             }
           }
           if (!ok) break;
+          if constexpr (GATHER) {
+            store_chunk_gather<GROUPED>(p, v, sch, m0 + c0, n0 + row);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int mm = m0 + c0 + i;
-            __half h = __float2half(__uint_as_float(v[i]));
-            if (!GROUPED) h = __hmul(h, sch);
-            if (mm < p.m) store_c(p, mm, n0 + row, h);
+            for (int i = 0; i < 16; ++i) {
+              const int mm = m0 + c0 + i;
+              __half h = __float2half(__uint_as_float(v[i]));
+              if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
+              if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+            }
           }
         }
         if (!ok) give_up(p, abort, 9);
@@ -516,12 +540,16 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
             }
           }
           if (!ok) break;
+          if constexpr (GATHER) {
+            store_chunk_gather<GROUPED>(p, v, sch, m0 + c0, n0 + row);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int mm = m0 + c0 + i;
-            __half h = __float2half(__uint_as_float(v[i]));
-            if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
-            if (mm < p.m) store_c(p, mm, n0 + row, h);
+            for (int i = 0; i < 16; ++i) {
+              const int mm = m0 + c0 + i;
+              __half h = __float2half(__uint_as_float(v[i]));
+              if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
+              if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+            }
           }
         }
       }

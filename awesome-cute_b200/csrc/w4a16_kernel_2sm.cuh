@@ -62,7 +62,7 @@ struct Bars2 {  // same offsets in both CTAs of the pair
 };
 static_assert(sizeof(Bars2) <= 1024, "barrier block");
 
-template <int TM, int KS_, bool GROUPED>
+template <int TM, int KS_, bool GROUPED, bool GATHER = false>
 __global__ void __launch_bounds__(Config2<TM, KS_>::THREADS, 1)
 w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                  const __grid_constant__ CUtensorMap tmS, const Params p) {
@@ -256,12 +256,16 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
             }
           }
           if (!ok) break;
+          if constexpr (GATHER) {
+            store_chunk_gather<GROUPED>(p, v, sch, m0 + c0, n0 + row);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int mm = m0 + c0 + i;
-            __half h = __float2half(__uint_as_float(v[i]));
-            if (!GROUPED) h = __hmul(h, sch);
-            if (mm < p.m) store_c(p, mm, n0 + row, h);
+            for (int i = 0; i < 16; ++i) {
+              const int mm = m0 + c0 + i;
+              __half h = __float2half(__uint_as_float(v[i]));
+              if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
+              if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+            }
           }
         }
         if (!ok) give_up(p, abort, 19);
@@ -336,12 +340,16 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
             }
           }
           if (!ok) break;
+          if constexpr (GATHER) {
+            store_chunk_gather<GROUPED>(p, v, sch, m0 + c0, n0 + row);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int mm = m0 + c0 + i;
-            __half h = __float2half(__uint_as_float(v[i]));
-            if (!GROUPED) h = __hmul(h, sch);
-            if (mm < p.m) store_c(p, mm, n0 + row, h);
+            for (int i = 0; i < 16; ++i) {
+              const int mm = m0 + c0 + i;
+              __half h = __float2half(__uint_as_float(v[i]));
+              if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
+              if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
+            }
           }
         }
       }

@@ -234,8 +234,15 @@ def run_ours(args):
     e1.record()
     torch.cuda.synchronize()
     barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_mine = e0.elapsed_time(e1)
+    ms_total = max_over_ranks(ms_mine)
     ms_per_step = ms_total / args.steps
+    per_rank_ms = None
+    if world > 1:
+        t = torch.zeros(world, device=dev, dtype=torch.float64)
+        t[rank] = ms_mine / args.steps
+        dist.all_reduce(t)
+        per_rank_ms = [round(float(x), 5) for x in t.tolist()]
     launches = args.steps * len(SHAPES)
     wbytes = weight_bytes(SHAPES)
     value = world * wbytes / (ms_per_step * 1e-3) / 1e9
@@ -381,12 +388,28 @@ def run_ours(args):
             e1.record()
             torch.cuda.synchronize()
             barrier()
+            fms_eager = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+            # and replayed from one CUDA graph, like `value` (the barrier's epoch counter lives on the device)
+            with torch.cuda.stream(side):
+                fstep(0)
+            side.synchronize()
+            fgraph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(fgraph, stream=side):
+                for i in range(args.steps):
+                    fstep(i)
+            fgraph.replay()
+            barrier()
+            e0.record()
+            fgraph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            barrier()
             fms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
             pkg.device_status(local)
             same = all(torch.equal(pbufs[li].local[:, rank * n:(rank + 1) * n], outs[li]) for li, (n, _) in enumerate(SHAPES))
             gathered["fused"] = {"value": world * wbytes / (fms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": fms,
-                                 "own_columns_match_plain_gemm": bool(same),
-                                 "note": "eager launches; epilogue stores to all ranks' buffers + barrier kernel per layer, no NCCL"}
+                                 "ms_per_step_eager": fms_eager, "own_columns_match_plain_gemm": bool(same),
+                                 "note": "K steps replayed from one CUDA graph; epilogue stores to all ranks' buffers + barrier kernel per layer, no NCCL"}
             for b in pbufs:
                 b.close()
         except Exception as exc:  # e.g. inter-process memory handles not permitted on this host
@@ -412,6 +435,8 @@ def run_ours(args):
                                     "sample": "one full step (4 GEMMs, M=16, 101 MB of packed weights), best of 2"}
         if gathered is not None:
             line["gathered"] = gathered
+        if per_rank_ms is not None:
+            line["per_rank_ms_per_step"] = per_rank_ms
         line.update(extras)
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -550,19 +575,45 @@ def run_sharded70b(args):
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 gms = float(t.item())
                 del full
+                ggms = None
+                try:  # the NCCL variant replayed from a CUDA graph as well, so that both arms are free of host launch cost
+                    ng = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(ng, stream=side):
+                        for i in range(reps):
+                            one(i)
+                            full = pkg.all_gather_columns(C, world)
+                    ng.replay()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    a.record()
+                    ng.replay()
+                    b.record()
+                    torch.cuda.synchronize()
+                    t = torch.tensor([a.elapsed_time(b) / reps], device=dev, dtype=torch.float64)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    ggms = float(t.item())
+                    del ng, full
+                except Exception:
+                    ggms = None
                 try:  # gathering epilogue + barrier kernel instead of the collective
                     pb = pkg.GatherBuffers(m, n_full, rank, world, dev)
 
                     def fused(i):
                         pkg.mul_gather(A, Bs[i % copies], ss[i % copies], ws, pb.dst_ptrs, rank)
                         pb.barrier()
-                    for i in range(2):
-                        fused(i)
+                    with torch.cuda.stream(side):
+                        for i in range(2):
+                            fused(i)
+                    side.synchronize()
+                    fg = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(fg, stream=side):
+                        for i in range(reps):
+                            fused(i)
+                    fg.replay()
                     torch.cuda.synchronize()
                     dist.barrier()
                     a.record()
-                    for i in range(reps):
-                        fused(i)
+                    fg.replay()
                     b.record()
                     torch.cuda.synchronize()
                     t = torch.tensor([a.elapsed_time(b) / reps], device=dev, dtype=torch.float64)
@@ -583,6 +634,8 @@ def run_sharded70b(args):
             if gms is not None:
                 res["gathered_us"] = gms * 1e3
                 res["gathered_tflops"] = flops / (gms * 1e-3) / 1e12
+                if ggms is not None:
+                    res["gathered_graph_us"] = ggms * 1e3
                 if fms is not None:
                     res["fused_gather_us"] = fms * 1e3
                     res["fused_gather_tflops"] = flops / (fms * 1e-3) / 1e12
