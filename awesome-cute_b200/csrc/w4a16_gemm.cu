@@ -763,6 +763,10 @@ struct PeerFlags {
 // counter.  The epoch lives on the device, so a captured launch keeps working when it is replayed.
 __global__ void peer_barrier_kernel(PeerFlags f, int world, int rank, uint64_t wait_ns, int *status) {
   const int lane = threadIdx.x;
+  // launched with programmatic stream serialisation: let the next kernel of the stream begin its prologue now (it
+  // orders itself behind this kernel with griddepcontrol.wait), then wait for the previous kernel to complete
+  sm100::pdl_launch_dependents();
+  sm100::pdl_wait_prior_grid();
   uint32_t *mine = f.p[rank];
   uint32_t e = 0;
   if (lane == 0) {
@@ -803,8 +807,19 @@ extern "C" int w4a16_peer_barrier(void *const *flags, int world, int rank, int d
     if (!ctx) return W4A16_ERR_CUDA;
     status = ctx->status;
   }
-  peer_barrier_kernel<<<1, 32, 0, st>>>(f, world, rank, (uint64_t)limit_ms * 1000000ull, status);
-  return cuda_ok(cudaGetLastError(), "barrier launch") ? W4A16_OK : W4A16_ERR_CUDA;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_ok(cudaLaunchKernelEx(&cfg, peer_barrier_kernel, f, world, rank, (uint64_t)limit_ms * 1000000ull, status),
+                 "barrier launch")
+             ? W4A16_OK
+             : W4A16_ERR_CUDA;
 }
 
 #ifdef W4A16_TRACE
