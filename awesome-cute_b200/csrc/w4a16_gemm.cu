@@ -144,7 +144,7 @@ void set_output(w4a16::Params &p, const Problem &pr) {
 
 template <int TM, int KS, bool GROUPED, bool GATHER>
 int launch_tc(const Problem &pr) {
-  using Cfg = w4a16::Config<TM, KS>;
+  using Cfg = w4a16::Config<TM, KS, GATHER>;
   auto kern = w4a16::w4a16_tc_kernel<TM, KS, GROUPED, GATHER>;
   // at least 116 KiB so that two CTAs can never share an SM (each one allocates all of TMEM)
   constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
@@ -252,7 +252,7 @@ int launch_tc(const Problem &pr) {
 // ---- large batches on CTA pairs (cta_group::2): see w4a16_kernel_2sm.cuh
 template <int TM, int KS, bool GROUPED, bool GATHER>
 int launch_tc2(const Problem &pr) {
-  using Cfg = w4a16::Config2<TM, KS>;
+  using Cfg = w4a16::Config2<TM, KS, GATHER>;
   auto kern = w4a16::w4a16_tc2_kernel<TM, KS, GROUPED, GATHER>;
   constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
   static bool attr_done[64] = {false};

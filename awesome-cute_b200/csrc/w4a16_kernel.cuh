@@ -113,10 +113,49 @@ __device__ __forceinline__ void store_chunk_gather(const Params &p, const uint32
   }
 }
 
+// Gathering epilogue, cooperative form used by the epilogue warps.  A warp owns 32 weight columns (its TMEM lane
+// quadrant), so on its own it can only write 64 contiguous bytes per output row, and peer stores of that size reach
+// less than half of the NVLink rate.  The four epilogue warps therefore stage each 16-row chunk of the 128-column tile
+// in shared memory and write it out by rows: 256 contiguous bytes per row, 8 bytes per lane, every destination.
+// Two slabs alternate; a warp may refill slab b for chunk c+2 once it has passed gfull[(c+1)&1], because every warp
+// reads chunk c before it arrives for chunk c+1.  Returns false when the (bounded) wait ran out.
+constexpr int GATHER_LD = TILE_N + 8;                       // slab row pitch in fp16 (272 bytes)
+constexpr int GATHER_SLAB_BYTES = 2 * 16 * GATHER_LD * 2 + 512;  // two 16-row slabs, padded to 9216
+template <bool GROUPED>
+__device__ __forceinline__ bool store_chunk_gather4(const Params &p, const uint32_t (&v)[16], __half sch, int mrow0, int n0,
+                                                    int quad, int lane, __half *slabs, uint32_t gfull_bar, int &gcount,
+                                                    volatile int *abort) {
+  const int buf = gcount & 1;
+  __half *sb = slabs + buf * 16 * GATHER_LD;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    __half h = __float2half(__uint_as_float(v[i]));
+    if (!GROUPED) h = __hmul(h, sch);  // after the fp16 convert, as in the plain epilogue
+    sb[i * GATHER_LD + quad * 32 + lane] = h;
+  }
+  __syncwarp();
+  if (lane == 0) sm100::mbar_arrive(gfull_bar + 8 * buf);
+  const bool ok = sm100::mbar_wait(gfull_bar + 8 * buf, (gcount >> 1) & 1, abort, p.wait_ns);
+  ++gcount;
+  if (!__all_sync(0xffffffffu, ok)) return false;
+  const size_t col = (size_t)p.c_col0 + n0 + lane * 4;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int r = quad + 4 * j, mm = mrow0 + r;
+    const uint2 val = *reinterpret_cast<const uint2 *>(sb + r * GATHER_LD + lane * 4);
+    if (mm < p.m) {
+      const size_t off = (size_t)mm * p.c_ld + col;
+      *reinterpret_cast<uint2 *>(p.C + off) = val;
+      for (int d = 0; d < p.n_extra; ++d) *reinterpret_cast<uint2 *>(p.C_extra[d] + off) = val;
+    }
+  }
+  return true;
+}
+
 // Tile configuration.  TM = batch tile (UMMA N); KS = k per pipeline stage.  The stage is the unit of
 // every hand-off; it is made large (256 k for small TM) because issuing a TMA costs the producer
 // 100+ clocks whatever its size, so bytes per TMA instruction is what bounds the load rate.
-template <int TM, int KS>
+template <int TM, int KS, bool GATHER = false>
 struct Config {
   static_assert(TM == 16 || TM == 32 || TM == 64 || TM == 128 || TM == 192, "batch tile");
   static_assert(KS == 64 || KS == 128 || KS == 256, "k per stage");
@@ -138,8 +177,9 @@ struct Config {
   static constexpr int WBUFS = WBUFS_RAW > 8 ? 8 : WBUFS_RAW;  // TMEM operand ring depth
   static_assert(WBUFS >= 2, "TMEM budget");
   static constexpr int BAR_BYTES = 1024;
+  static constexpr int GATHER_BYTES = GATHER ? GATHER_SLAB_BYTES : 0;   // output staging of the gathering epilogue
   static constexpr int SMEM_MAX = 227 * 1024;
-  static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - 1024) / STAGE_BYTES;
+  static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - GATHER_BYTES - 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static_assert(STAGES >= 3, "ring too shallow");
   // Two sets measured best on B200: a third adds eligible warps (+5 % on the largest decode shapes) but
@@ -147,7 +187,7 @@ struct Config {
   static constexpr int NSETS = 2;                            // dequant sets taking k-stages round-robin
   static constexpr int NDQ = 4 * NSETS;                      // dequant warps: NSETS sets of four
   static constexpr int THREADS = (NDQ + EPI_WARPS + 2) * 32;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024 /*align slack*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + GATHER_BYTES + 1024 /*align slack*/;
 };
 
 struct Bars {  // lives in shared memory
@@ -158,6 +198,7 @@ struct Bars {  // lives in shared memory
   uint64_t accfull[2];
   uint64_t accempty[2];
   uint64_t drain;
+  uint64_t gfull[2];     // gathering epilogue: all four epilogue warps have staged a 16-row chunk
   uint32_t tmem_base;
   int abort;
 };
@@ -198,11 +239,13 @@ template <int TM, int KS, bool GROUPED, bool GATHER = false>
 __global__ void __launch_bounds__(Config<TM, KS>::THREADS, 1)
 w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                 const __grid_constant__ CUtensorMap tmS, const Params p) {
-  using Cfg = Config<TM, KS>;
+  using Cfg = Config<TM, KS, GATHER>;
   using namespace sm100;
   constexpr int S = Cfg::STAGES;
   constexpr int NDQ = Cfg::NDQ;
-  constexpr bool HELP = TM >= 64;   // dequant warps help to finish a split tile (see the epilogue)
+  // dequant warps help to finish a split tile (see the epilogue); not in the gathering form, whose four epilogue
+  // warps write every chunk together
+  constexpr bool HELP = TM >= 64 && !GATHER;
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;
   constexpr uint32_t STAGE_TX = Cfg::W_BYTES + Cfg::A_BYTES + (GROUPED ? Cfg::S_BYTES : 0);
 
@@ -262,6 +305,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       for (int i = 0; i < 2; ++i) {
         mbar_init(smem_u32(&bars->accfull[i]), 1);
         mbar_init(smem_u32(&bars->accempty[i]), EPI_WARPS);
+        mbar_init(smem_u32(&bars->gfull[i]), EPI_WARPS);
       }
       mbar_init(smem_u32(&bars->drain), 1);
       bars->abort = 0;
@@ -471,6 +515,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     const int row = quad * 32 + lane;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
     pdl_wait_prior_grid();   // C and the partial-tile scratch may still be in use by the previous kernel
+    __half *slabs = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES);   // gathering form only
+    int gcount = 0;
     int seg = 0;
     for (int it = it_begin; it < it_end; ++seg) {
       const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
@@ -541,7 +587,10 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
           }
           if (!ok) break;
           if constexpr (GATHER) {
-            store_chunk_gather<GROUPED>(p, v, sch, m0 + c0, n0 + row);
+            if (!store_chunk_gather4<GROUPED>(p, v, sch, m0 + c0, n0, quad, lane, slabs, smem_u32(&bars->gfull[0]), gcount, abort)) {
+              ok = false;
+              break;
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {

@@ -19,7 +19,7 @@
 
 namespace w4a16 {
 
-template <int TM, int KS_ = 128>
+template <int TM, int KS_ = 128, bool GATHER = false>
 struct Config2 {
   static_assert(TM == 32 || TM == 64 || TM == 128 || TM == 192, "batch tile of the pair");
   static_assert(KS_ == 128 || KS_ == 256, "k per stage");
@@ -39,13 +39,14 @@ struct Config2 {
   static constexpr int WBUFS = WBUFS_RAW > 4 ? 4 : WBUFS_RAW;
   static_assert(WBUFS >= 2, "TMEM budget");
   static constexpr int BAR_BYTES = 1024;
+  static constexpr int GATHER_BYTES = GATHER ? GATHER_SLAB_BYTES : 0;
   static constexpr int SMEM_MAX = 227 * 1024;
-  static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - 1024) / STAGE_BYTES;
+  static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - GATHER_BYTES - 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static_assert(STAGES >= 3, "ring too shallow");
   static constexpr int NSETS = 2, NDQ = 8;
   static constexpr int THREADS = (NDQ + EPI_WARPS + 2) * 32;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + GATHER_BYTES + 1024;
 };
 
 struct Bars2 {  // same offsets in both CTAs of the pair
@@ -57,6 +58,7 @@ struct Bars2 {  // same offsets in both CTAs of the pair
   uint64_t accfull[2];   // accumulator complete (commit to both CTAs)                        (local)
   uint64_t accempty[2];  // accumulator drained by both CTAs' epilogue warps                  (used in the leader)
   uint64_t drain;
+  uint64_t gfull[2];     // gathering epilogue: this CTA's four epilogue warps have staged a chunk     (local)
   uint32_t tmem_base;
   int abort;
 };
@@ -66,11 +68,11 @@ template <int TM, int KS_, bool GROUPED, bool GATHER = false>
 __global__ void __launch_bounds__(Config2<TM, KS_>::THREADS, 1)
 w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                  const __grid_constant__ CUtensorMap tmS, const Params p) {
-  using Cfg = Config2<TM, KS_>;
+  using Cfg = Config2<TM, KS_, GATHER>;
   using namespace sm100;
   constexpr int S = Cfg::STAGES, NDQ = Cfg::NDQ, KS = Cfg::KS;
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;
-  constexpr bool HELP = TM >= 64;   // dequant warps help to finish a split tile (as in the single-CTA kernel)
+  constexpr bool HELP = TM >= 64 && !GATHER;   // dequant warps help to finish a split tile (as in the single-CTA kernel)
   constexpr uint32_t WS_TX = Cfg::W_BYTES + (GROUPED ? Cfg::S_BYTES : 0);
 
   extern __shared__ uint8_t smem_raw[];
@@ -118,6 +120,7 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars->accfull[i]), 1);
       mbar_init(smem_u32(&bars->accempty[i]), 2 * EPI_WARPS);
+      mbar_init(smem_u32(&bars->gfull[i]), EPI_WARPS);
     }
     mbar_init(smem_u32(&bars->drain), 1);
     bars->abort = 0;
@@ -277,6 +280,8 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     const int row = quad * 32 + lane;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
     pdl_wait_prior_grid();
+    __half *slabs = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES);   // gathering form only
+    int gcount = 0;
     int seg = 0;
     for (int it = it_begin; it < it_end; ++seg) {
       const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
@@ -341,7 +346,10 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
           }
           if (!ok) break;
           if constexpr (GATHER) {
-            store_chunk_gather<GROUPED>(p, v, sch, m0 + c0, n0 + row);
+            if (!store_chunk_gather4<GROUPED>(p, v, sch, m0 + c0, n0, quad, lane, slabs, smem_u32(&bars->gfull[0]), gcount, abort)) {
+              ok = false;
+              break;
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
