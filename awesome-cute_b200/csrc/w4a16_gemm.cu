@@ -15,6 +15,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <tuple>
 #include <utility>
 
 #include "../../include/marlin_cute.h"
@@ -176,41 +177,73 @@ int launch_tc(const Problem &pr) {
     grid = 1;                          // ... and only the CTA that finishes it is launched
   }
 
-  CUtensorMap tmB, tmA, tmS;
-  {  // weights: int32 [k/16][2n] viewed as [k/16][2n/32][32] so a 128-byte inner box can be swizzled
-    const cuuint64_t dims[3] = {32, (cuuint64_t)(2 * pr.n / 32), (cuuint64_t)(pr.k / 16)};
-    const cuuint64_t strides[2] = {128, (cuuint64_t)pr.n * 8};
-    const cuuint32_t box[3] = {32, 8, (cuuint32_t)(KS / 16)};
-    if (!encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, pr.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B"))
-      return W4A16_ERR_CUDA;
-  }
-  {  // activations: fp16 [m][k]; rows past m read as zero.  Preferred: the 3-D view [k/64][m][64] so that one
-     // box brings a whole stage as KS/64 swizzle atoms; if the driver refuses that stride order, 2-D boxes.
-    const cuuint64_t dims3[3] = {64, (cuuint64_t)pr.m, (cuuint64_t)(pr.k / 64)};
-    const cuuint64_t strides3[2] = {(cuuint64_t)pr.k * 2, 128};
-    const cuuint32_t box3[3] = {64, (cuuint32_t)TM, (cuuint32_t)Cfg::KCHUNKS};
-    p.a_box3d = 1;
-    if (Cfg::KCHUNKS == 1 ||
-        !encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pr.A, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B, "A3")) {
-      const cuuint64_t dims[2] = {(cuuint64_t)pr.k, (cuuint64_t)pr.m};
-      const cuuint64_t strides[1] = {(cuuint64_t)pr.k * 2};
-      const cuuint32_t box[2] = {64, (cuuint32_t)TM};
-      p.a_box3d = 0;
-      if (!encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A"))
-        return W4A16_ERR_CUDA;
+  // Tensor maps depend only on the operands' addresses and the shape, and encoding them is most of this function's
+  // host time, so they are kept per (B, A, s, m, n, k).
+  struct MapKey {
+    const void *B, *A, *s;
+    int m, n, k;
+    bool operator<(const MapKey &o) const {
+      return std::tie(B, A, s, m, n, k) < std::tie(o.B, o.A, o.s, o.m, o.n, o.k);
     }
-  }
-  if (GROUPED) {  // scales: fp16 [k/128][n]
-    const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
-    const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, (cuuint32_t)Cfg::GROUPS};
-    if (!encode(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
-      return W4A16_ERR_CUDA;
-  } else {
-    tmS = tmA;  // never read
-  }
+  };
+  struct Maps {
+    CUtensorMap b, a, s;
+    int a_box3d;
+  };
+  static std::map<MapKey, Maps> map_cache;
+  auto build_maps = [&](CUtensorMap &tmB, CUtensorMap &tmA, CUtensorMap &tmS, int &a_box3d) -> bool {
+    {  // weights: int32 [k/16][2n] viewed as [k/16][2n/32][32] so a 128-byte inner box can be swizzled
+      const cuuint64_t dims[3] = {32, (cuuint64_t)(2 * pr.n / 32), (cuuint64_t)(pr.k / 16)};
+      const cuuint64_t strides[2] = {128, (cuuint64_t)pr.n * 8};
+      const cuuint32_t box[3] = {32, 8, (cuuint32_t)(KS / 16)};
+      if (!encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, pr.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B"))
+        return false;
+    }
+    {  // activations: fp16 [m][k]; rows past m read as zero.  Preferred: the 3-D view [k/64][m][64] so that one
+       // box brings a whole stage as KS/64 swizzle atoms; if the driver refuses that stride order, 2-D boxes.
+      const cuuint64_t dims3[3] = {64, (cuuint64_t)pr.m, (cuuint64_t)(pr.k / 64)};
+      const cuuint64_t strides3[2] = {(cuuint64_t)pr.k * 2, 128};
+      const cuuint32_t box3[3] = {64, (cuuint32_t)TM, (cuuint32_t)Cfg::KCHUNKS};
+      a_box3d = 1;
+      if (Cfg::KCHUNKS == 1 ||
+          !encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pr.A, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B, "A3")) {
+        const cuuint64_t dims[2] = {(cuuint64_t)pr.k, (cuuint64_t)pr.m};
+        const cuuint64_t strides[1] = {(cuuint64_t)pr.k * 2};
+        const cuuint32_t box[2] = {64, (cuuint32_t)TM};
+        a_box3d = 0;
+        if (!encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A"))
+          return false;
+      }
+    }
+    if (GROUPED) {  // scales: fp16 [k/128][n]
+      const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
+      const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
+      const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, (cuuint32_t)Cfg::GROUPS};
+      if (!encode(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
+        return false;
+    } else {
+      tmS = tmA;  // never read
+    }
+
+    return true;
+  };
+  CUtensorMap tmB, tmA, tmS;
 
   std::lock_guard<std::mutex> lock(g_mu);
+  if (pr.fixed_partials) {   // the allocation-free entry point keeps nothing, on the host either
+    if (!build_maps(tmB, tmA, tmS, p.a_box3d)) return W4A16_ERR_CUDA;
+  } else {
+    const MapKey key{pr.B, pr.A, pr.s, pr.m, pr.n, pr.k};
+    auto it = map_cache.find(key);
+    if (it == map_cache.end()) {
+      Maps mp;
+      if (!build_maps(mp.b, mp.a, mp.s, mp.a_box3d)) return W4A16_ERR_CUDA;
+      if (map_cache.size() >= 512) map_cache.clear();
+      it = map_cache.emplace(key, mp).first;
+    }
+    tmB = it->second.b, tmA = it->second.a, tmS = it->second.s;
+    p.a_box3d = it->second.a_box3d;
+  }
   if (!attr_done[pr.dev]) {
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"))
       return W4A16_ERR_CUDA;

@@ -66,9 +66,9 @@ def mul(A, B, C, s, workspace, thread_k=-1, thread_n=-1, sms=-1, max_par=16, cut
         _check(err, prob_m, prob_n, prob_k, thread_k, thread_n, groupsize)
 
 
-def mul_host(A_host, B, C_host, s, workspace, A_stage, C_stage):
+def mul_host(A_host, B, C_host, s, workspace, A_stage, C_stage, stream=None):
     """`mul` for HOST activations / outputs (pinned torch tensors): copy in, multiply, copy out, all enqueued
-    on the current stream of B's device by one call into the library.  A_stage [m, k] and C_stage [m, n] are
+    on `stream` (a torch.cuda.Stream; default: the current stream of B's device) by one call into the library.  A_stage [m, k] and C_stage [m, n] are
     device staging tensors owned by the caller; B, s, workspace are device tensors as for `mul`.  Synchronise
     the stream before reading C_host."""
     prob_m, prob_k = A_host.shape
@@ -85,7 +85,8 @@ def mul_host(A_host, B, C_host, s, workspace, A_stage, C_stage):
         raise RuntimeError("device %d must be current" % dev)
     err = _L.w4a16_marlin_gemm_host(A_host.data_ptr(), B.data_ptr(), C_host.data_ptr(), s.data_ptr(), prob_m, prob_n,
                                     prob_k, workspace.data_ptr(), groupsize, dev,
-                                    torch.cuda.current_stream(dev).cuda_stream, A_stage.data_ptr(), C_stage.data_ptr())
+                                    (stream if stream is not None else torch.cuda.current_stream(dev)).cuda_stream,
+                                    A_stage.data_ptr(), C_stage.data_ptr())
     if err:
         _check(err, prob_m, prob_n, prob_k, -1, -1, groupsize)
 

@@ -89,12 +89,17 @@ class GatherBuffers:
         self._bytes = data_bytes + 64
         base = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
-        self._check(_L.w4a16_peer_alloc(self._bytes, ctypes.byref(base), handle), "w4a16_peer_alloc")
-        self._own = base.value
+        err = _L.w4a16_peer_alloc(self._bytes, ctypes.byref(base), handle)
+        self._own = base.value if not err else None
         self._opened = []
         handles = [None] * world
-        if world > 1:
-            dist.all_gather_object(handles, handle.raw, group=group)
+        if world > 1:   # every rank takes part in the exchange, also one whose allocation failed
+            dist.all_gather_object(handles, None if err else handle.raw, group=group)
+        self._check(err, "w4a16_peer_alloc")
+        if any(h is None for r, h in enumerate(handles) if r != rank):
+            _L.w4a16_peer_free(self._own)
+            self._own = None
+            raise RuntimeError("a peer rank could not allocate its gather buffer")
         bases = []
         for r in range(world):
             if r == rank:

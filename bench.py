@@ -267,8 +267,7 @@ def run_ours(args):
     def e2e_step(i):
         c = i % COPIES
         for li in range(len(SHAPES)):   # h2d copy of A, GEMM, d2h copy of C: one public call per GEMM
-            with torch.cuda.stream(lanes[li]):
-                pkg.mul_host(hA[li], layers[li][0][c], hC[li], layers[li][1][c], wss[li], acts[li], outs[li])
+            pkg.mul_host(hA[li], layers[li][0][c], hC[li], layers[li][1][c], wss[li], acts[li], outs[li], stream=lanes[li])
 
     for i in range(3):
         e2e_step(i)
@@ -371,8 +370,19 @@ def run_ours(args):
                     "note": "eager launches + NCCL all_gather_into_tensor of the fp16 outputs per layer"}
         # the same step with the gathering epilogue: the GEMM stores its tiles into every rank's output buffer over
         # peer-mapped memory; a one-warp barrier kernel per layer takes the place of the collective
+        pbufs, why = None, ""
         try:
             pbufs = [pkg.GatherBuffers(M_DECODE, world * n, rank, world, dev) for (n, _) in SHAPES]
+        except Exception as exc:  # e.g. inter-process memory handles not permitted on this host
+            why = str(exc)[:200]
+        flag = torch.tensor([1 if pbufs is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)     # the arm runs on all ranks or on none
+        if int(flag.item()) == 0:
+            gathered["fused"] = {"unavailable": why or "a peer rank could not map the gather buffers"}
+            pbufs = None
+        try:
+            if pbufs is None:
+                raise StopIteration
 
             def fstep(i):
                 c = i % COPIES
@@ -412,7 +422,9 @@ def run_ours(args):
                                  "note": "K steps replayed from one CUDA graph; epilogue stores to all ranks' buffers + barrier kernel per layer, no NCCL"}
             for b in pbufs:
                 b.close()
-        except Exception as exc:  # e.g. inter-process memory handles not permitted on this host
+        except StopIteration:
+            pass
+        except Exception as exc:
             gathered["fused"] = {"unavailable": str(exc)[:200]}
 
     sampler.active.clear()
@@ -595,8 +607,16 @@ def run_sharded70b(args):
                     del ng, full
                 except Exception:
                     ggms = None
-                try:  # gathering epilogue + barrier kernel instead of the collective
+                pb, why = None, "a peer rank could not map the gather buffers"
+                try:
                     pb = pkg.GatherBuffers(m, n_full, rank, world, dev)
+                except Exception as exc:
+                    why = str(exc)[:200]
+                flag = torch.tensor([1 if pb is not None else 0], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)     # the arm runs on all ranks or on none
+                try:  # gathering epilogue + barrier kernel instead of the collective
+                    if int(flag.item()) == 0:
+                        raise RuntimeError(why)
 
                     def fused(i):
                         pkg.mul_gather(A, Bs[i % copies], ss[i % copies], ws, pb.dst_ptrs, rank)
