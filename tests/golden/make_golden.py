@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ from the REFERENCE's own Python.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where a checkout of the reference project is at hand and pass its path:
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/path/to/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference
 
 It imports gemm/marlin_gemm/marlin.py (its missing ``marlin_lib`` extension is tolerated by the
 module itself, marlin.py:5-8) and follows ``gen_quant4`` of gemm/marlin_gemm/marlin_test.py:18-55 on
@@ -18,7 +18,9 @@ import numpy as np
 import torch
 import torch.nn as nn
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    sys.exit("usage: make_golden.py /path/to/reference")
+REF = sys.argv[1]
 sys.dont_write_bytecode = True
 sys.path.insert(0, os.path.join(REF, "gemm", "marlin_gemm"))
 import marlin  # noqa: E402  (the reference module)
