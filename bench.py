@@ -420,12 +420,13 @@ def run_ours(args):
             gathered["fused"] = {"value": world * wbytes / (fms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": fms,
                                  "ms_per_step_eager": fms_eager, "own_columns_match_plain_gemm": bool(same),
                                  "note": "K steps replayed from one CUDA graph; epilogue stores to all ranks' buffers + barrier kernel per layer, no NCCL"}
-            for b in pbufs:
-                b.close()
         except StopIteration:
             pass
         except Exception as exc:
             gathered["fused"] = {"unavailable": str(exc)[:200]}
+        if pbufs is not None:       # on every rank, whatever happened above: close() holds a collective
+            for b in pbufs:
+                b.close()
 
     sampler.active.clear()
     sampler.stop()
@@ -643,9 +644,10 @@ def run_sharded70b(args):
                     pkg.mul(A, Bs[(reps - 1) % copies], C, ss[(reps - 1) % copies], ws)
                     torch.cuda.synchronize()
                     fused_ok = bool(torch.equal(pb.local[:, rank * n:(rank + 1) * n], C))
-                    pb.close()
                 except Exception as exc:
                     fms, fused_ok = None, str(exc)[:200]
+                if int(flag.item()) == 1:   # on every rank, whatever happened above: close() holds a collective
+                    pb.close()
             flops = 2.0 * m * n_full * k
             wb = n_full * k / 2
             res = {"us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12, "weight_gbs": wb / (ms * 1e-3) / 1e9,
