@@ -84,7 +84,7 @@ class GatherBuffers:
     def __init__(self, m_max, n, rank, world, device, group=None):
         self.rank, self.world, self.m_max, self.n = rank, world, m_max, n
         self.device = torch.device(device)
-        self.dev = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.dev = self.device.index if self.device.index is not None else (torch.cuda.current_device() if torch.cuda.is_available() else 0)
         data_bytes = (m_max * n * 2 + 255) // 256 * 256
         self._bytes = data_bytes + 64
         base = ctypes.c_void_p()

@@ -88,3 +88,38 @@ def test_shard_constructor_rejects_ragged():
     except ValueError:
         return
     raise AssertionError("expected ValueError")
+
+
+def _gather_buffers_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        pkg = entry.load_package()
+        try:
+            pkg.GatherBuffers(16, 512, rank, world, "cpu")
+            q.put((rank, "no error"))
+        except RuntimeError as e:
+            q.put((rank, str(e)))
+        dist.barrier()      # both ranks are still in step: the failed set-up left no collective half done
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_buffers_fail_together_without_a_gpu():
+    """Without a CUDA device the peer allocation fails on every rank; each rank must still take part in the
+    handle exchange, raise, and stay in step with the others (no rank left waiting in a collective)."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_buffers_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=90) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    if torch.cuda.is_available():
+        return      # on a GPU machine the allocation succeeds; the path is covered by the GPU tests
+    for rank in (0, 1):
+        assert "w4a16_peer_alloc failed" in res[rank], res[rank]
