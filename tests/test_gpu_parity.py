@@ -397,14 +397,17 @@ def test_pair_kernel_dependent_chain_graph_replay():
         verify("graph %d" % rep)
 
 
-@pytest.mark.parametrize("m,nl,k", [(16, 512, 1024), (48, 256, 2048), (200, 512, 512), (1024, 2048, 4096)])
-def test_gathering_epilogue_on_one_gpu(m, nl, k):
+@pytest.mark.parametrize("m,nl,k,gs", [(16, 512, 1024, 128), (48, 256, 2048, 128), (200, 512, 512, 128),
+                                       (1024, 2048, 4096, 128), (33, 512, 1024, -1), (7, 256, 256, -1),
+                                       (1024, 4096, 4096, 128),      # CTA pairs, 128-row tiles
+                                       (960, 4096, 4096, -1)])       # CTA pairs, 192-row tiles, per-channel scales
+def test_gathering_epilogue_on_one_gpu(m, nl, k, gs):
     """The gathering GEMM with three destinations that all live on this GPU (the kernel only sees pointers): every
     destination receives this rank's columns, bit-identical to the plain GEMM, and nothing else is touched."""
     world, rank = 3, 1
-    An, q, sn = orc.make_problem(m, nl, k, 128, m + nl)
+    An, q, sn = orc.make_problem(m, nl, k, gs, m + nl)
     A, Bt, st = pack_problem(An, q, sn)
-    ref = orc.c_gemm(An, q, sn, 128)
+    ref = orc.c_gemm(An, q, sn, gs)
     ws = torch.zeros(nl // 128 * 16, dtype=torch.int, device=DEV)
     C = torch.zeros((m, nl), dtype=torch.half, device=DEV)
     pkg.mul(A, Bt, C, st, ws)
