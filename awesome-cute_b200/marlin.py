@@ -47,7 +47,7 @@ def mul(A, B, C, s, workspace, thread_k=-1, thread_n=-1, sms=-1, max_par=16, cut
     groupsize = -1 if s.shape[0] == 1 else prob_k // s.shape[0]
     if groupsize != -1 and groupsize * s.shape[0] != prob_k:
         raise RuntimeError("k=%d not compatible with %d groups." % (prob_k, s.shape[0]))
-    need = _L.w4a16_workspace_ints(prob_n, max_par)
+    need = prob_n // 128 * max_par      # w4a16_workspace_ints, computed here to keep the call path short
     if workspace.numel() < need:
         raise RuntimeError("workspace must be of size at least %d." % need)
     if not A.is_cuda:
@@ -76,8 +76,8 @@ def mul_host(A_host, B, C_host, s, workspace, A_stage, C_stage, stream=None):
     groupsize = -1 if s.shape[0] == 1 else prob_k // s.shape[0]
     if groupsize != -1 and groupsize * s.shape[0] != prob_k:
         raise RuntimeError("k=%d not compatible with %d groups." % (prob_k, s.shape[0]))
-    if workspace.numel() < _L.w4a16_workspace_ints(prob_n, 16):
-        raise RuntimeError("workspace must be of size at least %d." % _L.w4a16_workspace_ints(prob_n, 16))
+    if workspace.numel() < prob_n // 128 * 16:
+        raise RuntimeError("workspace must be of size at least %d." % (prob_n // 128 * 16))
     if A_host.is_cuda or C_host.is_cuda or not B.is_cuda:
         raise RuntimeError("mul_host() takes host activations/outputs and device weights.")
     dev = B.get_device()
