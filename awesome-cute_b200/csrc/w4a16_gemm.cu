@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <array>
 #include <cstdio>
 #include <cstdlib>
@@ -94,6 +95,18 @@ int sm_count(int dev) {
     g_sm_count[dev] = v;
   }
   return g_sm_count[dev];
+}
+
+int g_l2_bytes[64] = {0};
+
+int l2_bytes(int dev) {
+  if (dev < 0 || dev >= 64) return -1;
+  if (g_l2_bytes[dev] == 0) {
+    int v = 0;
+    if (!cuda_ok(cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev), "cudaDeviceGetAttribute")) return -1;
+    g_l2_bytes[dev] = v > 0 ? v : 1;
+  }
+  return g_l2_bytes[dev];
 }
 
 // Must be called with g_mu held.  Grows the partial-tile scratch when a launch needs more.
@@ -283,6 +296,35 @@ int launch_tc(const Problem &pr) {
 }
 
 // ---- large batches on CTA pairs (cta_group::2): see w4a16_kernel_2sm.cuh
+// W4A16_WAVES=0 in the environment keeps the CTA-pair kernel on contiguous stream-K ranges only (debugging aid)
+const bool g_use_waves = [] {
+  const char *e = std::getenv("W4A16_WAVES");
+  return !(e && e[0] == '0');
+}();
+// W4A16_MFAST=0 / 1 fixes the tile order of the whole-tile waves (1: the tile index runs over the batch tiles first);
+// unset, the launcher picks the order with the smaller estimated HBM traffic
+const int g_m_fast = [] {
+  const char *e = std::getenv("W4A16_MFAST");
+  return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1;
+}();
+
+// One wave of whole tiles is `pairs` consecutive tile indices.  With the weight-column index running first
+// (the reference's order, marlin_cute_trait.h:278-282) a wave shares few batch tiles and sweeps all weight columns:
+// activations are read once, weights once per wave unless L2 keeps them.  With the batch index running first it is
+// the other way round.  Whatever exceeds ~5/8 of L2 is taken to miss in proportion.  Returns 1 for batch-first.
+int pick_tile_order(int dev, double act_bytes, double weight_bytes, int n_tiles, int m_tiles, int pairs) {
+  if (g_m_fast >= 0) return g_m_fast;
+  const double cap = 0.625 * (double)l2_bytes(dev);
+  const double waves = (double)n_tiles * m_tiles / pairs;
+  auto traffic = [&](double bytes, double passes) {
+    const double miss = bytes <= cap ? 0.0 : 1.0 - cap / bytes;
+    return bytes * (1.0 + (passes - 1.0) * miss);
+  };
+  const double n_first = act_bytes + traffic(weight_bytes, std::min((double)m_tiles, waves));
+  const double m_first = weight_bytes + traffic(act_bytes, std::min((double)n_tiles, waves));
+  return m_first < 0.9 * n_first ? 1 : 0;
+}
+
 template <int TM, int KS, bool GROUPED, bool GATHER>
 int launch_tc2(const Problem &pr) {
   using Cfg = w4a16::Config2<TM, KS, GATHER>;
@@ -363,8 +405,18 @@ int launch_tc2(const Problem &pr) {
   if (pairs > max_pairs[pr.dev]) pairs = max_pairs[pr.dev];
   if (pairs > MAX_GRID / 2) pairs = MAX_GRID / 2;
   if (pairs > p.total_iters) pairs = p.total_iters;
-  p.iters_per_cta = (p.total_iters + pairs - 1) / pairs;     // per PAIR
-  pairs = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
+  // With two or more tiles per pair, all but the last one or two are taken whole and round-robin (tiles in flight at
+  // one time are neighbours and share their operands in L2); the rest is split by k-stages as before.
+  const int tiles = p.n_tiles * p.m_tiles;
+  if (g_use_waves && tiles >= 2 * pairs) {
+    p.dp_waves = tiles % pairs == 0 ? tiles / pairs : tiles / pairs - 1;
+    p.sk_tile0 = p.dp_waves * pairs;
+    p.total_iters = (tiles - p.sk_tile0) * p.k_iters;
+    p.m_fast = pick_tile_order(pr.dev, 2.0 * pr.m * pr.k, 0.5 * pr.n * pr.k, p.n_tiles, p.m_tiles, pairs);
+  }
+  p.iters_per_cta = p.total_iters > 0 ? (p.total_iters + pairs - 1) / pairs : 1;     // per PAIR
+  if (p.dp_waves == 0) pairs = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
+  p.workers = pairs;
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 192 * w4a16::TILE_N);
   if (!ctx) return W4A16_ERR_CUDA;
@@ -420,7 +472,8 @@ int dispatch_tc(const Problem &pr) {
   // ... when each pair gets at least ~32 k-stages: on smaller problems the single-CTA kernel's shorter start-up and
   // fix-up win (4096 x 4096 at m = 128: 17.5 us against 25.7 us)
   const long tm = pad192 * 100 <= pad128 * 106 ? 192 : 128;
-  const long pair_stages = (long)(pr.n / 256) * ((pr.m + tm - 1) / tm) * (pr.k / 128) / 74;
+  // (an explicit split count from the caller stands in for the 74 pairs of a whole B200)
+  const long pair_stages = (long)(pr.n / 256) * ((pr.m + tm - 1) / tm) * (pr.k / 128) / (pr.sms > 1 ? pr.sms / 2 : 74);
   if (g_use_pairs && k128 && pr.n % 256 == 0 && pair_stages >= 32 && !pr.fixed_partials && !pr.orphan_finisher) {
     int rc;
     if (tm == 192)

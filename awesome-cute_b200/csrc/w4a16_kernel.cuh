@@ -75,6 +75,10 @@ struct Params {
   int n_tiles, m_tiles, k_iters;        // k_iters = k / KS
   int total_iters, iters_per_cta;
   int a_box3d;                          // 1: tmA is the 3-D view (one box per stage), 0: 2-D (one box per 64 k)
+  // CTA-pair kernel only: data-parallel waves before the stream-K part.  Worker c of `workers` first runs the whole
+  // tiles c, c + workers, ... below sk_tile0 = dp_waves * workers; total_iters / iters_per_cta then describe the
+  // stream-K split of the tiles from sk_tile0 on.  m_fast: tile index runs over the batch tiles first.
+  int dp_waves, sk_tile0, workers, m_fast;
   const __half *s;                      // scales (read directly by the epilogue when per-channel)
   __half *C;
   uint32_t *partials;                   // [gridDim.x][TM][128] fp32 partial tiles; PARTIAL_IDLE between launches

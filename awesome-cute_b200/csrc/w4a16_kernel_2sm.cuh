@@ -64,6 +64,46 @@ struct Bars2 {  // same offsets in both CTAs of the pair
 };
 static_assert(sizeof(Bars2) <= 1024, "barrier block");
 
+// The segments (tile, k-stages [kb, ke)) of one pair, in the order it runs them: first whole tiles taken round-robin
+// (tile = pair, pair + workers, ... below sk_tile0), then its contiguous range of the stream-K part.  Round-robin
+// whole tiles keep the tiles in flight at one time next to each other (they share activation rows and weight columns,
+// so both stay in L2); with contiguous ranges alone the pairs are spread over the whole problem and a batch whose
+// activations exceed L2 is re-read from HBM for every tile.  The stream-K part at the end levels the last wave, as in
+// the reference's dense stream-K demo (gemm/streamk_gemm/dp_sk_block.h:82-173 splits full waves from the remainder).
+struct Walk {
+  int dp_tile, stride, sk_tile0, it, it_end, k_iters;
+  __device__ __forceinline__ Walk(const Params &p, int pair)
+      : dp_tile(pair), stride(p.workers), sk_tile0(p.sk_tile0), k_iters(p.k_iters) {
+    it = min(p.total_iters, pair * p.iters_per_cta);
+    it_end = min(p.total_iters, it + p.iters_per_cta);
+  }
+  __device__ __forceinline__ bool next(int &tile, int &kb, int &ke) {
+    if (dp_tile < sk_tile0) {
+      tile = dp_tile, kb = 0, ke = k_iters;
+      dp_tile += stride;
+      return true;
+    }
+    if (it >= it_end) return false;
+    const int t = it / k_iters;
+    kb = it - t * k_iters;
+    ke = min(k_iters, kb + (it_end - it));
+    tile = sk_tile0 + t;
+    it += ke - kb;
+    return true;
+  }
+};
+
+// tile index -> (256-column tile, batch tile)
+__device__ __forceinline__ void tile_nm(const Params &p, int tile, int &n_idx2, int &m_idx) {
+  if (p.m_fast) {
+    n_idx2 = tile / p.m_tiles;
+    m_idx = tile - n_idx2 * p.m_tiles;
+  } else {
+    m_idx = tile / p.n_tiles;
+    n_idx2 = tile - m_idx * p.n_tiles;
+  }
+}
+
 template <int TM, int KS_, bool GROUPED, bool GATHER = false>
 __global__ void __launch_bounds__(Config2<TM, KS_>::THREADS, 1)
 w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
@@ -88,10 +128,11 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   const int pair = blockIdx.x >> 1;
 
-  // ---- the PAIR's slice of the linearised (256-column tile, k-stage) space; p.n_tiles counts 256-column tiles
+  // ---- the PAIR's share: dp_waves whole tiles, then its slice of the linearised (256-column tile, k-stage) space of
+  // the stream-K part; p.n_tiles counts 256-column tiles
   const int it_begin = min(p.total_iters, pair * p.iters_per_cta);
   const int it_end = min(p.total_iters, it_begin + p.iters_per_cta);
-  const int nsteps = it_end - it_begin;
+  const int nsteps = p.dp_waves * p.k_iters + (it_end - it_begin);
 
   auto issue_weights = [&](int st, int n_idx2, int kk) {   // this CTA's 128 columns of the pair's tile
     const uint32_t full = smem_u32(&bars->wsfull[st]);
@@ -200,18 +241,18 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     if (warp == 0) { W4A16_BUCKET(4, d_full); W4A16_BUCKET(5, d_wempty); W4A16_BUCKET(6, d_work); }
     if (HELP) {
       // ---- help to finish the CTA's last tile if it is a split one (chunks 16*(1+set), +48, ... of this quadrant)
-      int seg = 0, l_tile = 0, l_kb = 1, l_ke = 0, l_seg = 0;
-      for (int it = it_begin; it < it_end; ++seg) {
-        l_tile = it / p.k_iters;
-        l_kb = it - l_tile * p.k_iters;
-        l_ke = min(p.k_iters, l_kb + (it_end - it));
-        l_seg = seg;
-        it += l_ke - l_kb;
+      int l_tile = 0, l_kb = 1, l_ke = 0, l_seg = -1;
+      {
+        Walk walk(p, pair);
+        int t, kb, ke;
+        while (walk.next(t, kb, ke)) l_tile = t, l_kb = kb, l_ke = ke, ++l_seg;
       }
-      if (it_end > it_begin && l_kb == 0 && l_ke < p.k_iters) {
-        const int n0 = (2 * (l_tile % p.n_tiles) + (int)rank) * TILE_N, m0 = (l_tile / p.n_tiles) * TM;
+      if (l_seg >= 0 && l_kb == 0 && l_ke < p.k_iters) {
+        int l_n, l_m;
+        tile_nm(p, l_tile, l_n, l_m);
+        const int n0 = (2 * l_n + (int)rank) * TILE_N, m0 = l_m * TM;
         const int acc = l_seg & 1;
-        const int last_pair = ((l_tile + 1) * p.k_iters - 1) / p.iters_per_cta;
+        const int last_pair = ((l_tile - p.sk_tile0 + 1) * p.k_iters - 1) / p.iters_per_cta;
         __half sch = __float2half(1.0f);
         if (!GROUPED) {
           const int c32 = row & 31;
@@ -282,15 +323,16 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     pdl_wait_prior_grid();
     __half *slabs = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES);   // gathering form only
     int gcount = 0;
-    int seg = 0;
-    for (int it = it_begin; it < it_end; ++seg) {
-      const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
-      const int ke = min(p.k_iters, kb + (it_end - it));
-      const int n0 = (2 * (tile % p.n_tiles) + (int)rank) * TILE_N, m0 = (tile / p.n_tiles) * TM;
+    Walk walk(p, pair);
+    int tile, kb, ke;
+    for (int seg = 0; walk.next(tile, kb, ke); ++seg) {
+      int n_idx2, m_idx;
+      tile_nm(p, tile, n_idx2, m_idx);
+      const int n0 = (2 * n_idx2 + (int)rank) * TILE_N, m0 = m_idx * TM;
       const int acc = seg & 1;
       const bool finisher = (kb == 0);
       // contributors are the same-rank CTAs of the following pairs: slots blockIdx.x + 2, + 4, ...
-      const int last_pair = (finisher && ke < p.k_iters) ? ((tile + 1) * p.k_iters - 1) / p.iters_per_cta : pair;
+      const int last_pair = (finisher && ke < p.k_iters) ? ((tile - p.sk_tile0 + 1) * p.k_iters - 1) / p.iters_per_cta : pair;
       const int ncontrib = last_pair - pair;
       __half sch = __float2half(1.0f);
       if (!GROUPED && finisher) {
@@ -365,37 +407,44 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->accempty[acc]), 0));
-      it += ke - kb;
     }
   } else if (warp == PRODUCER_WARP) {
     // =========================================================== TMA producer (one per CTA, each for its own halves)
-    int tile = it_begin / p.k_iters, kk = it_begin - tile * p.k_iters;
-    int nidx2 = tile % p.n_tiles, m0 = (tile / p.n_tiles) * TM;
     const int first = min(S, nsteps);
     int step = 0;
     {  // weights of the first ring-full: parameters, requested before the previous kernel of the stream is known done
-      int kk1 = kk, n1 = nidx2;
-      for (int i = 0; i < first; ++i) {
-        if (elect_one()) issue_weights(i, n1, kk1);
-        __syncwarp();
-        if (++kk1 == p.k_iters) { kk1 = 0; if (++n1 == p.n_tiles) n1 = 0; }
+      Walk walk(p, pair);
+      int tile, kb, ke, i = 0;
+      while (i < first && walk.next(tile, kb, ke)) {
+        int n_idx2, m_idx;
+        tile_nm(p, tile, n_idx2, m_idx);
+        for (int kk = kb; kk < ke && i < first; ++kk, ++i) {
+          if (elect_one()) issue_weights(i, n_idx2, kk);
+          __syncwarp();
+        }
       }
     }
     pdl_launch_dependents();
     pdl_wait_prior_grid();
-    for (; step < nsteps; ++step) {
-      const int st = step % S;
-      if (step >= first) {
-        if (!warp_wait(smem_u32(&bars->empty[st]), ((step / S) & 1) ^ 1, abort, p.wait_ns)) { give_up(p, abort, 15); break; }
-      }
-      if (elect_one()) {
-        if (step >= first) issue_weights(st, nidx2, kk);
-        issue_acts(st, m0, kk);
-      }
-      __syncwarp();
-      if (++kk == p.k_iters) {
-        kk = 0;
-        if (++nidx2 == p.n_tiles) { nidx2 = 0; m0 += TM; }
+    {
+      Walk walk(p, pair);
+      int tile, kb, ke;
+      bool ok = true;
+      while (ok && walk.next(tile, kb, ke)) {
+        int n_idx2, m_idx;
+        tile_nm(p, tile, n_idx2, m_idx);
+        const int m0 = m_idx * TM;
+        for (int kk = kb; kk < ke; ++kk, ++step) {
+          const int st = step % S;
+          if (step >= first) {
+            if (!warp_wait(smem_u32(&bars->empty[st]), ((step / S) & 1) ^ 1, abort, p.wait_ns)) { give_up(p, abort, 15); ok = false; break; }
+          }
+          if (elect_one()) {
+            if (step >= first) issue_weights(st, n_idx2, kk);
+            issue_acts(st, m0, kk);
+          }
+          __syncwarp();
+        }
       }
     }
     if (*abort) {   // unwinding: let this CTA's own weight copies land (activation bytes are counted in the leader)
@@ -413,9 +462,9 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     bool ok = true;
     long long m_afull = 0, m_wfull = 0, m_issue = 0, m_acc = 0;
     const uint32_t sA_u = smem_u32(sA);
-    for (int it = it_begin; it < it_end && ok; ++seg) {
-      const int tile = it / p.k_iters, kb = it - tile * p.k_iters;
-      const int ke = min(p.k_iters, kb + (it_end - it));
+    Walk walk(p, pair);
+    int tile, kb, ke;
+    for (; ok && walk.next(tile, kb, ke); ++seg) {
       const int acc = seg & 1;
       const long long ca = W4A16_CLK();
       if (!warp_wait(smem_u32(&bars->accempty[acc]), ((seg >> 1) & 1) ^ 1, abort, p.wait_ns)) { give_up(p, abort, 16); ok = false; break; }
@@ -448,7 +497,6 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
       }
       if (ok && elect_one()) tc_commit_pair(smem_u32(&bars->accfull[acc]));
       __syncwarp();
-      it += ke - kb;
     }
     W4A16_BUCKET(8, m_afull); W4A16_BUCKET(9, m_wfull); W4A16_BUCKET(10, m_issue); W4A16_BUCKET(11, m_acc); W4A16_BUCKET(3, step);
     if (!ok || *abort) {   // unwinding: no MMA may still be running when tensor memory is freed

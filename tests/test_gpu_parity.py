@@ -329,6 +329,46 @@ def test_cta_pair_split_counts(sms):
     run_problem(1000, 512, 1024, 64, 256, groupsize=-1, seed=sms + 7, sms=sms)
 
 
+@pytest.mark.parametrize("sms", [2, 6, 14])
+def test_cta_pair_whole_tile_waves_then_stream_k(sms):
+    """With two or more 256-column tiles per CTA pair the pairs first take whole tiles round-robin and split only the
+    last one or two waves by k-stages: 20 tiles over 1, 3 and 7 pairs (no remainder, 5 waves + 5 split tiles, 1 wave
+    + 13 split tiles), group and per-channel scales."""
+    run_problem(700, 1280, 2048, groupsize=128, seed=sms, sms=sms)
+    run_problem(700, 1280, 2048, groupsize=-1, seed=sms + 3, sms=sms)
+
+
+def test_cta_pair_waves_on_the_whole_gpu():
+    """192 tiles on all pairs of the device (one whole-tile wave, then stream-K); oracle on column windows."""
+    m, n, k, gs = 2304, 4096, 4096, 128
+    A, q, s = orc.make_problem(m, n, k, gs, 21)
+    At, Bt, st = pack_problem(A, q, s)
+    C = run_mul(At, Bt, st, m, n)
+    for n0 in (0, 1792, 4096 - 256):
+        ref = orc.c_gemm(A, np.ascontiguousarray(q[:, n0:n0 + 256]), np.ascontiguousarray(s[:, n0:n0 + 256]), gs)
+        check(C[:, n0:n0 + 256], ref, "window %d" % n0)
+
+
+def test_cta_pair_tile_order_switches():
+    """W4A16_MFAST=1 (tile index runs over the batch tiles first) and W4A16_WAVES=0 (contiguous stream-K ranges only)
+    are read once at load time: each runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys, os; sys.path.insert(0, os.getcwd()); sys.path.insert(0, os.path.join(os.getcwd(), 'tests'))\n"
+        "from gpu_common import run_problem\n"
+        "for sms in (6, 14):\n"
+        "    run_problem(700, 1280, 2048, groupsize=128, seed=sms, sms=sms)\n"
+        "    run_problem(700, 1280, 2048, groupsize=-1, seed=sms + 3, sms=sms)\n"
+        "print('ok')\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for switch in ({"W4A16_MFAST": "1"}, {"W4A16_WAVES": "0"}):
+        r = subprocess.run([sys.executable, "-c", code], cwd=root, env=dict(os.environ, **switch), capture_output=True,
+                           text=True, timeout=600)
+        assert r.returncode == 0 and "ok" in r.stdout, str(switch) + r.stdout[-2000:] + r.stderr[-2000:]
+
+
 @pytest.mark.parametrize("groupsize", [128, -1])
 def test_device_quantize_pack_is_bit_exact(groupsize):
     """Layer.pack on the device against the host packer (itself pinned to the reference packer's golden vectors),
