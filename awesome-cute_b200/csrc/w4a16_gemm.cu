@@ -471,7 +471,14 @@ int dispatch_tc(const Problem &pr) {
   // kernel: take them unless their row padding costs more than that.
   // ... when each pair gets at least ~32 k-stages: on smaller problems the single-CTA kernel's shorter start-up and
   // fix-up win (4096 x 4096 at m = 128: 17.5 us against 25.7 us)
-  const long tm = pad192 * 100 <= pad128 * 106 ? 192 : 128;
+  // The pair kernel runs a ragged last tile at its own width (UMMA N = its rows rounded up to 16), so padding costs
+  // nothing there; what a narrow tile still costs is its dequantisation, about 0.55 of a full 192-row tile's time.
+  // A full 128-row tile takes about 0.72 of a 192-row tile's time.
+  auto pair_cost = [&](int t, double full_cost) {
+    const int rem = pr.m % t;
+    return (pr.m / t) * full_cost + (rem ? std::max(((rem + 15) & ~15) / 192.0, 0.55) : 0.0);
+  };
+  const long tm = pair_cost(192, 1.0) <= pair_cost(128, 0.72) ? 192 : 128;
   // (an explicit split count from the caller stands in for the 74 pairs of a whole B200)
   const long pair_stages = (long)(pr.n / 256) * ((pr.m + tm - 1) / tm) * (pr.k / 128) / (pr.sms > 1 ? pr.sms / 2 : 74);
   if (g_use_pairs && k128 && pr.n % 256 == 0 && pair_stages >= 32 && !pr.fixed_partials && !pr.orphan_finisher) {

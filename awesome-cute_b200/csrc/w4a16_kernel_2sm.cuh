@@ -104,6 +104,15 @@ __device__ __forceinline__ void tile_nm(const Params &p, int tile, int &n_idx2, 
   }
 }
 
+// Batch rows the MMAs of a tile starting at row m0 cover: the rows that exist, rounded up to the UMMA N granule of 16.
+// A ragged last batch tile (and a batch smaller than the tile) then costs tensor time and fix-up traffic for its own
+// rows only.  Each CTA of the pair supplies half of them, so CTA r loads rows [m0 + r * width / 2, ...).
+template <int TM>
+__device__ __forceinline__ int tile_width(const Params &p, int m0) {
+  const int rows = min(TM, p.m - m0);
+  return max(16, (rows + 15) & ~15);
+}
+
 template <int TM, int KS_, bool GROUPED, bool GATHER = false>
 __global__ void __launch_bounds__(Config2<TM, KS_>::THREADS, 1)
 w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
@@ -144,7 +153,7 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
   auto issue_acts = [&](int st, int m0, int kk) {          // this CTA's half of the activation rows
     const uint32_t leader_full = map_to_cta(smem_u32(&bars->afull[st]), 0);
     if (rank == 0) mbar_expect_tx(smem_u32(&bars->afull[st]), 2 * Cfg::A_BYTES);
-    tma_load_3d_pair(smem_u32(sA) + st * Cfg::A_BYTES, &tmA, 0, m0 + (int)rank * Cfg::HALF_ROWS, kk * Cfg::KCHUNKS, leader_full);
+    tma_load_3d_pair(smem_u32(sA) + st * Cfg::A_BYTES, &tmA, 0, m0 + (int)rank * (tile_width<TM>(p, m0) >> 1), kk * Cfg::KCHUNKS, leader_full);
   };
 
   // ---- prologue
@@ -263,8 +272,9 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
         tc_fence_after();
         const uint64_t t0 = globaltimer_ns();
         const uint32_t t_acc = tmem + ((uint32_t)(quad * 32) << 16) + acc * Cfg::ACC_STRIDE;
+        const int width = tile_width<TM>(p, m0);
 #pragma unroll 1
-        for (int c0 = 16 * (1 + set); c0 < TM && ok; c0 += 48) {
+        for (int c0 = 16 * (1 + set); c0 < width && ok; c0 += 48) {
           uint32_t v[16];
           tmem_ld_32x32b_x16(t_acc + c0, v);
           tc_wait_ld();
@@ -346,8 +356,9 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
       const uint64_t t0 = ncontrib > 0 ? globaltimer_ns() : 0ull;
       constexpr int FLY = 2;
       const int c_step = (HELP && finisher && ncontrib > 0) ? 48 : 16;   // the dequant warps take the other chunks
+      const int width = tile_width<TM>(p, m0);
 #pragma unroll 1
-      for (int c0 = 0; c0 < TM && ok; c0 += c_step) {
+      for (int c0 = 0; c0 < width && ok; c0 += c_step) {
         uint32_t v[16];
         tmem_ld_32x32b_x16(t_lane + acc * Cfg::ACC_STRIDE + c0, v);
         tc_wait_ld();
@@ -457,7 +468,6 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     }
   } else if (rank == 0) {
     // =========================================================== MMA issuer: the leader's warp, for both CTAs
-    constexpr uint32_t idesc = make_idesc_f16_f32(2 * TILE_N, TM);
     int step = 0, seg = 0;
     bool ok = true;
     long long m_afull = 0, m_wfull = 0, m_issue = 0, m_acc = 0;
@@ -465,6 +475,9 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     Walk walk(p, pair);
     int tile, kb, ke;
     for (; ok && walk.next(tile, kb, ke); ++seg) {
+      int n_idx2, m_idx;
+      tile_nm(p, tile, n_idx2, m_idx);
+      const uint32_t idesc = make_idesc_f16_f32(2 * TILE_N, tile_width<TM>(p, m_idx * TM));   // UMMA N = the tile's own rows
       const int acc = seg & 1;
       const long long ca = W4A16_CLK();
       if (!warp_wait(smem_u32(&bars->accempty[acc]), ((seg >> 1) & 1) ^ 1, abort, p.wait_ns)) { give_up(p, abort, 16); ok = false; break; }
