@@ -22,6 +22,7 @@ SYMBOLS = {
     "w4a16_marlin_gemm_host": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp]),
     "w4a16_workspace_ints": (_i, [_i, _i]),
     "w4a16_device_status": (_i, [_i, _vp]),
+    "w4a16_release_stream": (_i, [_i, _vp]),
     "w4a16_selftest_unanswered_wait": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i]),
     "w4a16_last_cuda_error": (ctypes.c_char_p, []),
     "w4a16_pack_weights": (_i, [_vp, _i, _i, _vp]),

@@ -18,11 +18,13 @@
 #include <string>
 #include <tuple>
 #include <utility>
+#include <vector>
 
 #include "../../include/marlin_cute.h"
 #include "../../include/w4a16.h"
 #include "w4a16_kernel.cuh"
 #include "w4a16_kernel_2sm.cuh"
+#include "w4a16_kernel_decode.cuh"
 
 namespace {
 
@@ -32,6 +34,13 @@ thread_local std::string g_last_error;
 const bool g_use_pdl = [] {
   const char *e = std::getenv("W4A16_PDL");
   return !(e && e[0] == '0');
+}();
+
+// W4A16_WAIT_MS in the environment shortens (or lengthens, up to 5000) the limit of every device-side wait (debugging aid)
+const uint64_t g_wait_ns = [] {
+  const char *e = std::getenv("W4A16_WAIT_MS");
+  const long v = e ? std::atol(e) : 0;
+  return (v >= 1 && v <= 5000) ? (uint64_t)v * 1000000ull : w4a16::WAIT_LIMIT_NS;
 }();
 
 bool cuda_ok(cudaError_t e, const char *what) {
@@ -80,6 +89,9 @@ struct StreamCtx {
   uint32_t *partials = nullptr;  // fp32 partial-tile slots, all PARTIAL_IDLE (0xff bytes) between launches
   size_t partial_slots = 0;
   int *status = nullptr;
+  // Earlier, smaller scratch blocks.  They stay allocated (idle pattern intact) until w4a16_release_stream: a launch
+  // captured in a CUDA graph keeps pointing at the block it was captured with.
+  std::vector<std::pair<uint32_t *, size_t>> retired;
 };
 constexpr int MAX_GRID = 256;
 
@@ -109,7 +121,10 @@ int l2_bytes(int dev) {
   return g_l2_bytes[dev];
 }
 
-// Must be called with g_mu held.  Grows the partial-tile scratch when a launch needs more.
+// Must be called with g_mu held.  The scratch is sized by need: the first block covers every launch of up to 64 batch
+// rows on this device (one slot row per CTA row: SMs x 64 x 128 fp32, 4.8 MB on a 148-SM part), larger batch tiles
+// grow it (SMs x 192 x 128 fp32 = 14.5 MB at most).  Growing allocates, which CUDA refuses while a stream is being
+// captured: run a problem of the size once before capturing it.
 StreamCtx *get_ctx(int dev, cudaStream_t stream, size_t need_slots) {
   StreamCtx &c = g_ctx[{dev, stream}];
   if (!c.status) {
@@ -117,15 +132,18 @@ StreamCtx *get_ctx(int dev, cudaStream_t stream, size_t need_slots) {
     if (!cuda_ok(cudaMemset(c.status, 0, sizeof(int)), "cudaMemset(status)")) return nullptr;
   }
   if (c.partial_slots < need_slots) {
-    if (c.partials) {
-      if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return nullptr;
-      cudaFree(c.partials);
-      c.partials = nullptr;
-      c.partial_slots = 0;
+    const int nsm = sm_count(dev);
+    const size_t floor_slots = (size_t)(nsm > 0 ? nsm : MAX_GRID) * 64 * w4a16::TILE_N;
+    const size_t slots = std::max(need_slots, floor_slots);
+    uint32_t *blk = nullptr;
+    if (!cuda_ok(cudaMalloc(&blk, sizeof(uint32_t) * slots), "cudaMalloc(partials)")) return nullptr;
+    if (!cuda_ok(cudaMemset(blk, 0xff, sizeof(uint32_t) * slots), "cudaMemset(partials)")) {
+      cudaFree(blk);
+      return nullptr;
     }
-    if (!cuda_ok(cudaMalloc(&c.partials, sizeof(uint32_t) * need_slots), "cudaMalloc(partials)")) return nullptr;
-    if (!cuda_ok(cudaMemset(c.partials, 0xff, sizeof(uint32_t) * need_slots), "cudaMemset(partials)")) return nullptr;
-    c.partial_slots = need_slots;
+    if (c.partials) c.retired.emplace_back(c.partials, c.partial_slots);
+    c.partials = blk;
+    c.partial_slots = slots;
   }
   return &c;
 }
@@ -141,7 +159,7 @@ struct Problem {
   size_t fixed_slots = 0;
   // set only by the bounded-wait self-test: launch CTA 0 alone, so that it waits for partial tiles nobody writes
   bool orphan_finisher = false;
-  uint64_t wait_ns = w4a16::WAIT_LIMIT_NS;
+  uint64_t wait_ns = g_wait_ns;
   // set only by the gathering entry point: C is [m][c_ld], this GEMM's columns start at c_col0, and every finished
   // tile also goes to the same place of n_extra further buffers
   int c_ld = 0, c_col0 = 0, n_extra = 0;
@@ -156,12 +174,115 @@ void set_output(w4a16::Params &p, const Problem &pr) {
   p.C_extra = reinterpret_cast<__half *const *>(pr.C_extra);
 }
 
-template <int TM, int KS, bool GROUPED, bool GATHER>
-int launch_tc(const Problem &pr) {
-  using Cfg = w4a16::Config<TM, KS, GATHER>;
-  auto kern = w4a16::w4a16_tc_kernel<TM, KS, GROUPED, GATHER>;
+// ---- tensor maps.  They depend only on the operands' addresses, the shape and the kernel's box sizes, and encoding
+// them is most of a launch's host time, so they are kept: key (B, A, s, m, n, k, k per stage, activation rows per box).
+struct Maps {
+  CUtensorMap b, a, s;
+  int a_box3d;
+};
+struct MapKey {
+  const void *B, *A, *s;
+  int m, n, k, ks, a_rows, grouped;
+  bool operator<(const MapKey &o) const {
+    return std::tie(B, A, s, m, n, k, ks, a_rows, grouped) < std::tie(o.B, o.A, o.s, o.m, o.n, o.k, o.ks, o.a_rows, o.grouped);
+  }
+};
+std::map<MapKey, Maps> g_maps;   // guarded by g_mu
+
+bool build_maps(const Problem &pr, int ks, int a_rows, bool grouped, Maps &mp) {
+  {  // weights: int32 [k/16][2n] viewed as [k/16][2n/32][32] so a 128-byte inner box can be swizzled
+    const cuuint64_t dims[3] = {32, (cuuint64_t)(2 * pr.n / 32), (cuuint64_t)(pr.k / 16)};
+    const cuuint64_t strides[2] = {128, (cuuint64_t)pr.n * 8};
+    const cuuint32_t box[3] = {32, 8, (cuuint32_t)(ks / 16)};
+    if (!encode(&mp.b, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, pr.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B"))
+      return false;
+  }
+  {  // activations: fp16 [m][k]; rows past m read as zero.  Preferred: the 3-D view [k/64][m][64] so that one
+     // box brings a whole stage as ks/64 swizzle atoms; if the driver refuses that stride order, 2-D boxes.
+    const cuuint64_t dims3[3] = {64, (cuuint64_t)pr.m, (cuuint64_t)(pr.k / 64)};
+    const cuuint64_t strides3[2] = {(cuuint64_t)pr.k * 2, 128};
+    const cuuint32_t box3[3] = {64, (cuuint32_t)a_rows, (cuuint32_t)(ks / 64)};
+    mp.a_box3d = 1;
+    if (ks == 64 ||
+        !encode(&mp.a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pr.A, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B, "A3")) {
+      const cuuint64_t dims[2] = {(cuuint64_t)pr.k, (cuuint64_t)pr.m};
+      const cuuint64_t strides[1] = {(cuuint64_t)pr.k * 2};
+      const cuuint32_t box[2] = {64, (cuuint32_t)a_rows};
+      mp.a_box3d = 0;
+      if (!encode(&mp.a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A"))
+        return false;
+    }
+  }
+  if (grouped) {  // scales: fp16 [k/128][n]
+    const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
+    const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, (cuuint32_t)(ks >= 128 ? ks / 128 : 1)};
+    if (!encode(&mp.s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
+      return false;
+  } else {
+    mp.s = mp.a;  // never read
+  }
+  return true;
+}
+
+// Takes g_mu for the lookup only.
+bool get_maps(const Problem &pr, int ks, int a_rows, bool grouped, Maps &out) {
+  if (pr.fixed_partials) return build_maps(pr, ks, a_rows, grouped, out);  // the allocation-free entry point keeps nothing, on the host either
+  const MapKey key{pr.B, pr.A, pr.s, pr.m, pr.n, pr.k, ks, a_rows, grouped ? 1 : 0};
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    Maps mp;
+    if (!build_maps(pr, ks, a_rows, grouped, mp)) return false;
+    if (g_maps.size() >= 1024) g_maps.clear();
+    it = g_maps.emplace(key, mp).first;
+  }
+  out = it->second;
+  return true;
+}
+
+// scratch + status word of this launch (library-owned per (device, stream), or the built-in array)
+bool get_scratch(const Problem &pr, size_t need_slots, w4a16::Params &p) {
+  if (pr.fixed_partials) {
+    if (need_slots > pr.fixed_slots) {
+      g_last_error = "problem needs " + std::to_string(need_slots) + " partial-tile slots, the built-in scratch holds " +
+                     std::to_string(pr.fixed_slots);
+      return false;
+    }
+    p.partials = pr.fixed_partials;
+    p.status = pr.fixed_status;
+    return true;
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  StreamCtx *ctx = get_ctx(pr.dev, pr.stream, need_slots);
+  if (!ctx) return false;
+  p.partials = ctx->partials;
+  p.status = ctx->status;
+  return true;
+}
+
+// the kernels behind launch_single, as traits
+template <int TM_, int KS_, bool GROUPED_, bool GATHER_>
+struct GeneralKernel {
+  using Cfg = w4a16::Config<TM_, KS_, GATHER_>;
+  static constexpr int TM = TM_, KS = KS_, THREADS = Cfg::THREADS, SMEM = Cfg::SMEM_BYTES;
+  static constexpr bool GROUPED = GROUPED_;
+  static auto kernel() { return w4a16::w4a16_tc_kernel<TM_, KS_, GROUPED_, GATHER_>; }
+};
+template <bool GROUPED_, bool GATHER_>
+struct DecodeKernel {
+  using Cfg = w4a16::DecodeConfig<GATHER_>;
+  static constexpr int TM = Cfg::TM, KS = Cfg::KS, THREADS = Cfg::THREADS, SMEM = Cfg::SMEM_BYTES;
+  static constexpr bool GROUPED = GROUPED_;
+  static auto kernel() { return w4a16::w4a16_decode_kernel<GROUPED_, GATHER_>; }
+};
+
+// One CTA per SM, persistent, stream-K over (128-column tile, k-stage).
+template <class K>
+int launch_single(const Problem &pr) {
+  auto kern = K::kernel();
   // at least 116 KiB so that two CTAs can never share an SM (each one allocates all of TMEM)
-  constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
+  constexpr int smem = K::SMEM > 116 * 1024 ? K::SMEM : 116 * 1024;
   static bool attr_done[64] = {false};
 
   const int nsm = sm_count(pr.dev);
@@ -170,8 +291,8 @@ int launch_tc(const Problem &pr) {
   w4a16::Params p{};
   p.m = pr.m, p.n = pr.n, p.k = pr.k;
   p.n_tiles = pr.n / w4a16::TILE_N;
-  p.m_tiles = (pr.m + TM - 1) / TM;
-  p.k_iters = pr.k / KS;
+  p.m_tiles = (pr.m + K::TM - 1) / K::TM;
+  p.k_iters = pr.k / K::KS;
   const long total = (long)p.n_tiles * p.m_tiles * p.k_iters;
   if (total > 0x7fffffffL) return W4A16_ERR_ARG;
   p.total_iters = (int)total;
@@ -190,92 +311,14 @@ int launch_tc(const Problem &pr) {
     grid = 1;                          // ... and only the CTA that finishes it is launched
   }
 
-  // Tensor maps depend only on the operands' addresses and the shape, and encoding them is most of this function's
-  // host time, so they are kept per (B, A, s, m, n, k).
-  struct MapKey {
-    const void *B, *A, *s;
-    int m, n, k;
-    bool operator<(const MapKey &o) const {
-      return std::tie(B, A, s, m, n, k) < std::tie(o.B, o.A, o.s, o.m, o.n, o.k);
-    }
-  };
-  struct Maps {
-    CUtensorMap b, a, s;
-    int a_box3d;
-  };
-  static std::map<MapKey, Maps> map_cache;
-  auto build_maps = [&](CUtensorMap &tmB, CUtensorMap &tmA, CUtensorMap &tmS, int &a_box3d) -> bool {
-    {  // weights: int32 [k/16][2n] viewed as [k/16][2n/32][32] so a 128-byte inner box can be swizzled
-      const cuuint64_t dims[3] = {32, (cuuint64_t)(2 * pr.n / 32), (cuuint64_t)(pr.k / 16)};
-      const cuuint64_t strides[2] = {128, (cuuint64_t)pr.n * 8};
-      const cuuint32_t box[3] = {32, 8, (cuuint32_t)(KS / 16)};
-      if (!encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, pr.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B"))
-        return false;
-    }
-    {  // activations: fp16 [m][k]; rows past m read as zero.  Preferred: the 3-D view [k/64][m][64] so that one
-       // box brings a whole stage as KS/64 swizzle atoms; if the driver refuses that stride order, 2-D boxes.
-      const cuuint64_t dims3[3] = {64, (cuuint64_t)pr.m, (cuuint64_t)(pr.k / 64)};
-      const cuuint64_t strides3[2] = {(cuuint64_t)pr.k * 2, 128};
-      const cuuint32_t box3[3] = {64, (cuuint32_t)TM, (cuuint32_t)Cfg::KCHUNKS};
-      a_box3d = 1;
-      if (Cfg::KCHUNKS == 1 ||
-          !encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pr.A, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B, "A3")) {
-        const cuuint64_t dims[2] = {(cuuint64_t)pr.k, (cuuint64_t)pr.m};
-        const cuuint64_t strides[1] = {(cuuint64_t)pr.k * 2};
-        const cuuint32_t box[2] = {64, (cuuint32_t)TM};
-        a_box3d = 0;
-        if (!encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A"))
-          return false;
-      }
-    }
-    if (GROUPED) {  // scales: fp16 [k/128][n]
-      const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
-      const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
-      const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, (cuuint32_t)Cfg::GROUPS};
-      if (!encode(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
-        return false;
-    } else {
-      tmS = tmA;  // never read
-    }
-
-    return true;
-  };
-  CUtensorMap tmB, tmA, tmS;
-
-  std::lock_guard<std::mutex> lock(g_mu);
-  if (pr.fixed_partials) {   // the allocation-free entry point keeps nothing, on the host either
-    if (!build_maps(tmB, tmA, tmS, p.a_box3d)) return W4A16_ERR_CUDA;
-  } else {
-    const MapKey key{pr.B, pr.A, pr.s, pr.m, pr.n, pr.k};
-    auto it = map_cache.find(key);
-    if (it == map_cache.end()) {
-      Maps mp;
-      if (!build_maps(mp.b, mp.a, mp.s, mp.a_box3d)) return W4A16_ERR_CUDA;
-      if (map_cache.size() >= 512) map_cache.clear();
-      it = map_cache.emplace(key, mp).first;
-    }
-    tmB = it->second.b, tmA = it->second.a, tmS = it->second.s;
-    p.a_box3d = it->second.a_box3d;
-  }
-  if (!attr_done[pr.dev]) {
+  Maps mp;
+  if (!get_maps(pr, K::KS, K::TM, K::GROUPED, mp)) return W4A16_ERR_CUDA;
+  p.a_box3d = mp.a_box3d;
+  if (!get_scratch(pr, (size_t)grid * K::TM * w4a16::TILE_N, p)) return pr.fixed_partials ? W4A16_ERR_ARG : W4A16_ERR_CUDA;
+  if (!attr_done[pr.dev]) {   // (idempotent: a race between two host threads sets the same value twice)
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"))
       return W4A16_ERR_CUDA;
     attr_done[pr.dev] = true;
-  }
-  if (pr.fixed_partials) {
-    const size_t need = (size_t)grid * TM * w4a16::TILE_N;
-    if (need > pr.fixed_slots) {
-      g_last_error = "problem needs " + std::to_string(need) + " partial-tile slots, the built-in scratch holds " +
-                     std::to_string(pr.fixed_slots);
-      return W4A16_ERR_ARG;
-    }
-    p.partials = pr.fixed_partials;
-    p.status = pr.fixed_status;
-  } else {
-    StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 192 * w4a16::TILE_N);
-    if (!ctx) return W4A16_ERR_CUDA;
-    p.partials = ctx->partials;
-    p.status = ctx->status;
   }
   // Programmatic dependent launch: this kernel may begin (prologue, weight prefetch) while the previous kernel of
   // the stream is finishing; it orders itself behind that kernel with griddepcontrol.wait before it reads
@@ -283,7 +326,7 @@ int launch_tc(const Problem &pr) {
   // launch is an ordinary stream-ordered one.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3((unsigned)Cfg::THREADS);
+  cfg.blockDim = dim3((unsigned)K::THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = pr.stream;
   cudaLaunchAttribute attr[1];
@@ -291,8 +334,13 @@ int launch_tc(const Problem &pr) {
   attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, tmB, tmA, tmS, p), "kernel launch")) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, p), "kernel launch")) return W4A16_ERR_CUDA;
   return W4A16_OK;
+}
+
+template <int TM, int KS, bool GROUPED, bool GATHER>
+int launch_tc(const Problem &pr) {
+  return launch_single<GeneralKernel<TM, KS, GROUPED, GATHER>>(pr);
 }
 
 // ---- large batches on CTA pairs (cta_group::2): see w4a16_kernel_2sm.cuh
@@ -349,31 +397,6 @@ int launch_tc2(const Problem &pr) {
   p.wait_ns = pr.wait_ns;
   p.a_box3d = 1;
 
-  CUtensorMap tmB, tmA, tmS;
-  {
-    const cuuint64_t dims[3] = {32, (cuuint64_t)(2 * pr.n / 32), (cuuint64_t)(pr.k / 16)};
-    const cuuint64_t strides[2] = {128, (cuuint64_t)pr.n * 8};
-    const cuuint32_t box[3] = {32, 8, (cuuint32_t)(Cfg::KS / 16)};
-    if (!encode(&tmB, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, pr.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "B"))
-      return W4A16_ERR_CUDA;
-  }
-  {  // each CTA of the pair loads half of the tile's rows
-    const cuuint64_t dims3[3] = {64, (cuuint64_t)pr.m, (cuuint64_t)(pr.k / 64)};
-    const cuuint64_t strides3[2] = {(cuuint64_t)pr.k * 2, 128};
-    const cuuint32_t box3[3] = {64, (cuuint32_t)Cfg::HALF_ROWS, (cuuint32_t)Cfg::KCHUNKS};
-    if (!encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pr.A, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_128B, "A3"))
-      return W4A16_ERR_CUDA;
-  }
-  if (GROUPED) {
-    const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)(pr.k / 128)};
-    const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, (cuuint32_t)Cfg::GROUPS};
-    if (!encode(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.s, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "s"))
-      return W4A16_ERR_CUDA;
-  } else {
-    tmS = tmA;
-  }
-
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3((unsigned)Cfg::THREADS);
   cfg.dynamicSmemBytes = smem;
@@ -388,16 +411,18 @@ int launch_tc2(const Problem &pr) {
   cfg.attrs = attr;
   cfg.numAttrs = 2;
 
-  std::lock_guard<std::mutex> lock(g_mu);
-  if (!attr_done[pr.dev]) {
-    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"))
-      return W4A16_ERR_CUDA;
-    // the finisher of a split tile needs its contributors co-resident: never launch more pairs than fit at once
-    cfg.gridDim = dim3((unsigned)(nsm & ~1));
-    int clusters = 0;
-    if (!cuda_ok(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg), "cudaOccupancyMaxActiveClusters")) return W4A16_ERR_CUDA;
-    max_pairs[pr.dev] = clusters;
-    attr_done[pr.dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!attr_done[pr.dev]) {
+      if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"))
+        return W4A16_ERR_CUDA;
+      // the finisher of a split tile needs its contributors co-resident: never launch more pairs than fit at once
+      cfg.gridDim = dim3((unsigned)(nsm & ~1));
+      int clusters = 0;
+      if (!cuda_ok(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg), "cudaOccupancyMaxActiveClusters")) return W4A16_ERR_CUDA;
+      max_pairs[pr.dev] = clusters;
+      attr_done[pr.dev] = true;
+    }
   }
   if (max_pairs[pr.dev] < 1) return -2;   // no CTA pair can be scheduled here: the caller takes the single-CTA kernel
   int pairs = pr.sms > 0 ? pr.sms / 2 : nsm / 2;
@@ -418,17 +443,25 @@ int launch_tc2(const Problem &pr) {
   if (p.dp_waves == 0) pairs = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
   p.workers = pairs;
   cfg.gridDim = dim3((unsigned)(2 * pairs));
-  StreamCtx *ctx = get_ctx(pr.dev, pr.stream, (size_t)MAX_GRID * 192 * w4a16::TILE_N);
-  if (!ctx) return W4A16_ERR_CUDA;
-  p.partials = ctx->partials;
-  p.status = ctx->status;
-  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, tmB, tmA, tmS, p), "kernel launch (CTA pairs)")) return W4A16_ERR_CUDA;
+  Maps mp;   // each CTA of the pair loads half of the tile's activation rows
+  if (!get_maps(pr, Cfg::KS, Cfg::HALF_ROWS, GROUPED, mp)) return W4A16_ERR_CUDA;
+  if (!mp.a_box3d) {
+    g_last_error = "the CTA-pair kernel needs the 3-D activation view";
+    return W4A16_ERR_CUDA;
+  }
+  if (!get_scratch(pr, (size_t)2 * pairs * TM * w4a16::TILE_N, p)) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, p), "kernel launch (CTA pairs)")) return W4A16_ERR_CUDA;
   return W4A16_OK;
 }
 
 // W4A16_PAIRS=0 in the environment keeps large batches on the single-CTA kernel (debugging aid)
 const bool g_use_pairs = [] {
   const char *e = std::getenv("W4A16_PAIRS");
+  return !(e && e[0] == '0');
+}();
+// W4A16_DECODE=0 in the environment keeps batches of up to 16 rows on the general kernel (debugging aid, A/B timing)
+const bool g_use_decode = [] {
+  const char *e = std::getenv("W4A16_DECODE");
   return !(e && e[0] == '0');
 }();
 
@@ -447,9 +480,16 @@ int launch_tc2_g(const Problem &pr) {
   return pr.groupsize == 128 ? launch_tc2<TM, KS, true, false>(pr) : launch_tc2<TM, KS, false, false>(pr);
 }
 
+int launch_decode_g(const Problem &pr) {
+  if (pr.c_ld > 0)
+    return pr.groupsize == 128 ? launch_single<DecodeKernel<true, true>>(pr) : launch_single<DecodeKernel<false, true>>(pr);
+  return pr.groupsize == 128 ? launch_single<DecodeKernel<true, false>>(pr) : launch_single<DecodeKernel<false, false>>(pr);
+}
+
 int dispatch_tc(const Problem &pr) {
   // batch tile = UMMA N; the k per stage is as deep as the activation tile allows (fewer, larger TMAs)
   const bool k256 = (pr.k % 256) == 0, k128 = (pr.k % 128) == 0;
+  if (pr.m <= 16 && k256 && g_use_decode) return launch_decode_g(pr);   // the HBM-bound case has a kernel of its own
   if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
   // 17..32 rows on CTA pairs as well (+12-16 %)
   if (g_use_pairs && pr.m > 16 && pr.m <= 32 && k256 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
@@ -554,6 +594,19 @@ int check_problem(int prob_m, int prob_n, int prob_k, int groupsize, int &thread
   return W4A16_OK;
 }
 
+// The launch, the per-device kernel attributes and the built-in scratch all belong to the CURRENT device, which the
+// caller must have made `dev` (the reference's launcher has the same rule: it never calls cudaSetDevice and uses
+// `dev` only for the SM count, marlin_cute_kernel.cu:37-38).  Checked on every call: it is one thread-local read.
+bool device_is_current(int dev) {
+  int cur = -1;
+  if (!cuda_ok(cudaGetDevice(&cur), "cudaGetDevice")) return false;
+  if (cur != dev) {
+    g_last_error = "device " + std::to_string(dev) + " must be the current device (current is " + std::to_string(cur) + ")";
+    return false;
+  }
+  return true;
+}
+
 int gemm_entry(bool simt, const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n, int prob_k,
                void *workspace, int groupsize, int dev, cudaStream_t stream, int thread_k, int thread_n, int sms,
                int max_par) {
@@ -568,6 +621,7 @@ int gemm_entry(bool simt, const void *A, const void *B, void *C, const void *s, 
        reinterpret_cast<uintptr_t>(s)) & 15)
     return W4A16_ERR_ARG;
   if (dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  if (!device_is_current(dev)) return W4A16_ERR_ARG;
   Problem pr{A, B, s, C, prob_m, prob_n, prob_k, groupsize, dev, sms, stream};
   return simt ? launch_simt(pr) : dispatch_tc(pr);
 }
@@ -610,23 +664,6 @@ extern "C" int w4a16_marlin_gemm_host(const void *A_host, const void *B, void *C
   return W4A16_OK;
 }
 
-// Self-test of the bounded waits: the GEMM is set up so that the CTA finishing tile 0 expects a partial tile
-// from a CTA that is never launched.  Nothing faults or spins on: after limit_ms the kernel records a status,
-// unwinds and returns, and w4a16_device_status reports W4A16_ERR_TIMEOUT.  C is left undefined.
-extern "C" int w4a16_selftest_unanswered_wait(const void *A, const void *B, void *C, const void *s, int prob_m,
-                                              int prob_n, int prob_k, int groupsize, int dev, void *stream,
-                                              int limit_ms) {
-  int tk = -1, tn = -1;
-  if (prob_m <= 0 || prob_n <= 0 || prob_k <= 0 || limit_ms <= 0 || limit_ms > 5000) return W4A16_ERR_ARG;
-  const int chk = check_problem(prob_m, prob_n, prob_k, groupsize, tk, tn);
-  if (chk != W4A16_OK) return chk;
-  if (!A || !B || !C || !s || dev < 0 || dev >= 64) return W4A16_ERR_ARG;
-  Problem pr{A, B, s, C, prob_m, prob_n, prob_k, groupsize, dev, -1, static_cast<cudaStream_t>(stream)};
-  pr.orphan_finisher = true;
-  pr.wait_ns = (uint64_t)limit_ms * 1000000ull;
-  return dispatch_tc(pr);
-}
-
 extern "C" int w4a16_marlin_gemm_simt(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n,
                                       int prob_k, void *workspace, int groupsize, int dev, void *stream, int thread_k,
                                       int thread_n, int sms, int max_par) {
@@ -655,12 +692,6 @@ BuiltinScratch g_builtin[64];
 int builtin_setup(int dev, cudaStream_t stream) {
   BuiltinScratch &b = g_builtin[dev];
   if (b.ready) return W4A16_OK;
-  int cur = -1;
-  if (!cuda_ok(cudaGetDevice(&cur), "cudaGetDevice")) return W4A16_ERR_CUDA;
-  if (cur != dev) {
-    g_last_error = "device " + std::to_string(dev) + " must be the current device (current is " + std::to_string(cur) + ")";
-    return W4A16_ERR_ARG;
-  }
   void *pp = nullptr, *ps = nullptr;
   if (!cuda_ok(cudaGetSymbolAddress(&pp, g_builtin_partials), "cudaGetSymbolAddress(partials)")) return W4A16_ERR_CUDA;
   if (!cuda_ok(cudaGetSymbolAddress(&ps, g_builtin_status), "cudaGetSymbolAddress(status)")) return W4A16_ERR_CUDA;
@@ -694,9 +725,42 @@ extern "C" int w4a16_marlin_gemm_builtin_scratch(const void *A, const void *B, v
        reinterpret_cast<uintptr_t>(s)) & 15)
     return W4A16_ERR_ARG;
   if (dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  // every call, not only the first: the symbol addresses looked up for `dev` mean nothing on another device
+  if (!device_is_current(dev)) return W4A16_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Problem pr{A, B, s, C, prob_m, prob_n, prob_k, groupsize, dev, sms, st};
   {
+    std::lock_guard<std::mutex> lock(g_mu);
+    const int rc = builtin_setup(dev, st);
+    if (rc != W4A16_OK) return rc;
+    pr.fixed_partials = g_builtin[dev].partials;
+    pr.fixed_status = g_builtin[dev].status;
+    pr.fixed_slots = BUILTIN_SLOTS;
+  }
+  return dispatch_tc(pr);
+}
+
+// Self-test of the bounded waits: the GEMM is set up so that the CTA finishing tile 0 expects a partial tile
+// from a CTA that is never launched.  Nothing faults or spins on: after the limit the kernel records a status,
+// unwinds and returns, and w4a16_device_status reports W4A16_ERR_TIMEOUT.  C is left undefined.
+// limit_ms < 0 runs the same on the built-in scratch of w4a16_marlin_gemm_builtin_scratch for -limit_ms ms.
+extern "C" int w4a16_selftest_unanswered_wait(const void *A, const void *B, void *C, const void *s, int prob_m,
+                                              int prob_n, int prob_k, int groupsize, int dev, void *stream,
+                                              int limit_ms) {
+  int tk = -1, tn = -1;
+  const bool builtin = limit_ms < 0;
+  if (builtin) limit_ms = -limit_ms;
+  if (prob_m <= 0 || prob_n <= 0 || prob_k <= 0 || limit_ms <= 0 || limit_ms > 5000) return W4A16_ERR_ARG;
+  if (builtin && prob_m > BUILTIN_MAX_M) return W4A16_ERR_ARG;
+  const int chk = check_problem(prob_m, prob_n, prob_k, groupsize, tk, tn);
+  if (chk != W4A16_OK) return chk;
+  if (!A || !B || !C || !s || dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  if (!device_is_current(dev)) return W4A16_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Problem pr{A, B, s, C, prob_m, prob_n, prob_k, groupsize, dev, -1, st};
+  pr.orphan_finisher = true;
+  pr.wait_ns = (uint64_t)limit_ms * 1000000ull;
+  if (builtin) {
     std::lock_guard<std::mutex> lock(g_mu);
     const int rc = builtin_setup(dev, st);
     if (rc != W4A16_OK) return rc;
@@ -735,8 +799,7 @@ extern "C" int w4a16_device_status(int dev, void *stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return W4A16_ERR_CUDA;
   int *status = nullptr;
-  uint32_t *partials = nullptr;
-  size_t slots = 0;
+  std::vector<std::pair<uint32_t *, size_t>> blocks;
   bool launched_here = false;
   {
     std::lock_guard<std::mutex> lock(g_mu);
@@ -744,8 +807,8 @@ extern "C" int w4a16_device_status(int dev, void *stream) {
     if (it != g_ctx.end()) {
       launched_here = true;
       status = it->second.status;
-      partials = it->second.partials;
-      slots = it->second.partial_slots;
+      blocks = it->second.retired;
+      if (it->second.partials) blocks.emplace_back(it->second.partials, it->second.partial_slots);
     }
   }
   if (!launched_here) return builtin_status(dev);  // no library-allocated scratch on this (device, stream)
@@ -754,9 +817,28 @@ extern "C" int w4a16_device_status(int dev, void *stream) {
   if (word == 0) return builtin_status(dev);
   if (!cuda_ok(cudaMemset(status, 0, sizeof(int)), "cudaMemset(status)")) return W4A16_ERR_CUDA;
   // a kernel that gave up may have left partial-tile slots written
-  if (partials && !cuda_ok(cudaMemset(partials, 0xff, sizeof(uint32_t) * slots), "cudaMemset(partials)")) return W4A16_ERR_CUDA;
+  for (auto &b : blocks)
+    if (!cuda_ok(cudaMemset(b.first, 0xff, sizeof(uint32_t) * b.second), "cudaMemset(partials)")) return W4A16_ERR_CUDA;
   g_last_error = "device-side wait timed out at site " + std::to_string(word >> 8);
   return W4A16_ERR_TIMEOUT;
+}
+
+extern "C" int w4a16_release_stream(int dev, void *stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return W4A16_ERR_CUDA;
+  StreamCtx c;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_ctx.find({dev, st});
+    if (it == g_ctx.end()) return W4A16_OK;
+    c = it->second;
+    g_ctx.erase(it);
+  }
+  bool ok = true;
+  for (auto &b : c.retired) ok &= cuda_ok(cudaFree(b.first), "cudaFree(partials)");
+  if (c.partials) ok &= cuda_ok(cudaFree(c.partials), "cudaFree(partials)");
+  if (c.status) ok &= cuda_ok(cudaFree(c.status), "cudaFree(status)");
+  return ok ? W4A16_OK : W4A16_ERR_CUDA;
 }
 
 extern "C" const char *w4a16_last_cuda_error(void) { return g_last_error.c_str(); }
@@ -789,6 +871,7 @@ extern "C" int w4a16_marlin_gemm_gather(const void *A, const void *B, const void
   }
   if (bits & 15) return W4A16_ERR_ARG;
   if (dev < 0 || dev >= 64) return W4A16_ERR_ARG;
+  if (!device_is_current(dev)) return W4A16_ERR_ARG;
   if ((long)n_local * world > 0x7fffffffL) return W4A16_ERR_ARG;
   Problem pr{A, B, s, dst[rank], prob_m, n_local, prob_k, groupsize, dev, -1, static_cast<cudaStream_t>(stream)};
   pr.c_ld = n_local * world;
@@ -896,7 +979,7 @@ extern "C" int w4a16_peer_barrier(void *const *flags, int world, int rank, int d
   int *status = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_mu);
-    StreamCtx *ctx = get_ctx(dev, st, (size_t)MAX_GRID * 192 * w4a16::TILE_N);
+    StreamCtx *ctx = get_ctx(dev, st, 0);
     if (!ctx) return W4A16_ERR_CUDA;
     status = ctx->status;
   }

@@ -2,30 +2,37 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1] at its M = 16 point): one STEP is the four Llama-2-7B linear layers
+Workload (the decode configuration the metric is quoted on): one STEP is the four Llama-2-7B linear layers
 (N,K) = (12288,4096), (4096,4096), (22016,4096), (4096,11008), group size 128, batch M = 16, fp16
 activations ~N(0,1), int4 codes uniform with zero-point 8, fp16 scales uniform in [0.005, 0.02]:
 four GEMM launches that stream 101 MB of packed weights.  Weights rotate over 3 resident copies
-(303 MB > 126 MB L2) so every launch reads its weights from HBM.
+(303 MB > 126 MB L2) so every launch reads its weights from HBM.  The reference's own shape list for these
+layers is gemm/marlin_gemm/marlin_test.py:133-142 and gemm/marlin_gemm/marlin_profiling.py:89-94.
 
-metric / value   weight HBM GB/s = packed-weight bytes of all ranks / time (CUDA events, max over ranks);
-                 the K timed steps are replayed from one CUDA graph so the figure is the kernels', not
-                 Python's launch path
+metric / value   weight HBM GB/s = packed-weight bytes of all ranks / time.  K steps are captured in one CUDA graph
+                 (so the figure is the kernels', not Python's launch path); the graph is replayed R >= 5 times back to
+                 back (R chosen so that the timed region is >= 50 ms), every replay between its own pair of CUDA
+                 events on the launching stream; ms_per_step = median replay / K per rank, then the max over ranks
 e2e              the same metric through the public call `mul_host()` (C ABI w4a16_marlin_gemm_host) with HOST
                  buffers: per GEMM the activations are copied from pinned host memory and the output copied
-                 back inside the call, plain launches, no graph;
-                 weights stay resident on the device as a layer's parameters do (marlin.py:82-83)
+                 back inside the call, plain launches, no graph; weights stay resident on the device as a layer's
+                 parameters do (marlin.py:82-83).  `value`: the step's four layers as independent requests on four
+                 streams; `value_single_stream`: the same calls in order on one stream
 roofline         HBM bound: algorithmic bytes (weights + scales + A + C) per launch / mean launch time
-cpu_baseline     the CPU oracle (dequantise + fp32 GEMM, all host threads) on one full step
-prefill          extra: TFLOP/s at M = 4096 on the same four shapes (BASELINE.json configs[2])
-N > 1            every rank runs the same per-GPU workload on its own column shard of a layer N times as
-                 wide (weak scaling, no collective on the data path); `gathered` reports the step with
-                 an NCCL all-gather of the fp16 outputs added
+max_err / bound  inside `roofline` and `e2e`: one real packed layer (seeded codes and scales, packed by the shipped
+                 packer) run through the same call and compared with the CPU oracle, outside every timed region
+cpu_baseline     the CPU oracle (dequantise + fp32 GEMM, all host cores) on one full step
+extras           decode sweep M in {1..64}, prefill M in {1024, 4096}, the large-K shape 8192 x 28672
+sharded70b       last key of the line: the Llama-2-70B gate-up 57344x8192 and down 8192x28672 layers column-sharded
+                 over the N ranks (strong scaling), M in {16, 4096}: plain, + NCCL all-gather, + gathering epilogue
+N > 1            `value`: every rank runs the same per-GPU workload on its own column shard of a layer N times as
+                 wide (weak scaling, no collective on the data path)
 --impl reference the reference has no runnable CPU or sm_100 implementation of this path, so this arm
-                 times the CPU restatement of its algorithm (oracle/, kind "port") on rank 0 only
+                 times the CPU restatement of its algorithm (oracle/, kind "port") on rank 0 only, on all host cores
 """
 import argparse
 import json
+import math
 import os
 import sys
 import threading
@@ -38,15 +45,26 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 SHAPES = [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)]   # (N, K) of Llama-2-7B linears
+LAYERS70 = [("gate_up", 57344, 8192), ("down", 8192, 28672)]          # Llama-2-70B, column-sharded over the ranks
 GROUP = 128
 M_DECODE = 16
 COPIES = 3
 METRIC = "w4a16_weight_hbm_gbs_m16"
 UNIT = "GB/s"
-# DRAM bytes per launch from one ncu capture of each of the step's four kernels (mean of 26.16, 9.21, 46.68 and
-# 23.76 MB); the capture command and the per-shape figures are in profiles/decode_m16_dram_traffic.md.
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from one ncu capture of each of the step's
+# four kernels: 26.16, 9.21, 46.68 and 23.76 MB, mean 26.45 MB.  It is a property of the access pattern (every
+# weight byte is read once), re-captured whenever the decode kernel's loads change.
 NCU_DRAM_BYTES_PER_LAUNCH = 26.45e6
 WORKLOAD = "llama2-7b linears (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)}, M=16, g128"
+# the same for both arms, so that their lines describe one configuration
+CONFIG = {
+    "workload": WORKLOAD,
+    "l2": "weights rotate over %d resident copies (303 MB > 126 MB L2)" % COPIES,
+    "timing": "K steps per CUDA graph, >= 5 back-to-back replays (>= 50 ms), median replay, max over ranks",
+    "parallelism": "one column shard per GPU, no collective on the data path",
+}
+MIN_REPLAYS = 5
+MIN_TIMED_MS = 50.0
 
 
 def weight_bytes(shapes):
@@ -69,7 +87,10 @@ def load_peaks():
 
 # ----------------------------------------------------------------------------------------------------- clocks
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML while the measurements run."""
+    """Samples SM clock and throttle reasons through NVML while timed regions run (every 20 ms: a timed region is
+    at least 50 ms of back-to-back graph replays, and the poll itself stays out of the launch path's way)."""
+
+    PERIOD_S = 0.02
 
     def __init__(self, index):
         super().__init__(daemon=True)
@@ -102,7 +123,7 @@ class ClockSampler(threading.Thread):
                     for bit, name in names.items():
                         if mask & bit:
                             self.reasons.add(name)
-                time.sleep(0.002)
+                time.sleep(self.PERIOD_S)
         except Exception as e:  # NVML missing: report that instead of clocks
             self.reasons.add("nvml_unavailable:%s" % type(e).__name__)
 
@@ -116,9 +137,10 @@ class ClockSampler(threading.Thread):
 
 
 # ----------------------------------------------------------------------------------------------------- reference arm
-def cpu_time_step(threads_note=True, reps=1):
-    """One full step (four GEMMs, M = 16) through the CPU oracle; returns (seconds, threads)."""
+def cpu_time_step(reps=1):
+    """One full step (four GEMMs, M = 16) through the CPU oracle on all host cores; returns (seconds, threads)."""
     from oracle import oracle as orc
+    threads = orc.use_all_cores()
     probs = [orc.make_problem(M_DECODE, n, k, GROUP, seed=i) for i, (n, k) in enumerate(SHAPES)]
     orc.c_gemm(*probs[1], GROUP)  # warm the thread pool
     best = None
@@ -128,7 +150,7 @@ def cpu_time_step(threads_note=True, reps=1):
             orc.c_gemm(A, q, s, GROUP)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    return best, orc.num_threads()
+    return best, threads
 
 
 def run_reference(args):
@@ -136,10 +158,11 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import oracle as orc
+    threads = orc.use_all_cores()    # not the OMP_NUM_THREADS=1 a multi-rank launcher exports
     probs = [orc.make_problem(M_DECODE, n, k, GROUP, seed=i) for i, (n, k) in enumerate(SHAPES)]
-    for _ in range(args.warmup):
+    for _ in range(max(args.warmup, 1)):
         orc.c_gemm(*probs[1], GROUP)
-    steps = min(args.steps, 20)   # bounded: one step is ~0.5 s of CPU work on 8 cores
+    steps = min(args.steps, 20)   # bounded: one step is ~0.1-0.5 s of CPU work
     t0 = time.perf_counter()
     for _ in range(steps):
         for (A, q, s) in probs:
@@ -149,10 +172,10 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference algorithm (dequantise + fp32 GEMM); "
-                   "the reference ships no CPU kernel and its CUDA kernels do not run on sm_100"},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": CONFIG,
+        "note": "CPU restatement of the reference algorithm (dequantise + fp32 GEMM): the reference ships no CPU kernel "
+                "and its CUDA kernels do not run on sm_100",
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": "%d full steps (4 GEMMs, M=16, 101 MB of packed weights each)" % steps},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -161,34 +184,128 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------------------- our arm
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
+class Ctx:
+    """Device, ranks, streams and the timing helpers every leg uses."""
 
-    import __graft_entry__ as entry
-    pkg = entry.load_package()   # raises if libw4a16.so is missing: there is no fallback
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import __graft_entry__ as entry
+        self.torch, self.dist = torch, dist
+        self.pkg = entry.load_package()   # raises if libw4a16.so is missing: there is no fallback
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.peaks = load_peaks()
+        self.gen = torch.Generator(device=self.dev).manual_seed(1234 + self.rank)
+        self.side = torch.cuda.Stream(device=self.dev)
+        self.sampler = ClockSampler(self.local)
+        self.sampler.start()
 
-    peaks = load_peaks()
-    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    def close(self):
+        self.sampler.stop()
+        if self.world > 1:
+            self.dist.destroy_process_group()
 
-    def make_layer(n, k, copies):
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, x):
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], device=self.dev, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def per_rank(self, x):
+        if self.world == 1:
+            return [x]
+        t = self.torch.zeros(self.world, device=self.dev, dtype=self.torch.float64)
+        t[self.rank] = x
+        self.dist.all_reduce(t)
+        return [float(v) for v in t.tolist()]
+
+    def make_layer(self, n, k, copies):
         """Random packed operands straight on the device: any int32 is a valid packed word (eight
         uniform codes) and the scale permutation of uniform values is uniform."""
-        Bs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen)
+        torch = self.torch
+        Bs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=self.dev, generator=self.gen)
               for _ in range(copies)]
-        ss = [(torch.rand((k // GROUP, n), device=dev, generator=gen) * 0.015 + 0.005).half() for _ in range(copies)]
+        ss = [(torch.rand((k // GROUP, n), device=self.dev, generator=self.gen) * 0.015 + 0.005).half() for _ in range(copies)]
         return Bs, ss
 
-    layers = [make_layer(n, k, COPIES) for (n, k) in SHAPES]
-    acts = [torch.randn((M_DECODE, k), device=dev, generator=gen).half() for (_, k) in SHAPES]
+    def randn_half(self, m, k):
+        return self.torch.randn((m, k), device=self.dev, generator=self.gen).half()
+
+    def capture(self, fn, reps, warm=1):
+        """fn(i) for i in range(reps) captured into one CUDA graph (after `warm` eager calls on the capture stream)."""
+        torch = self.torch
+        with torch.cuda.stream(self.side):
+            for i in range(warm):
+                fn(i)
+        self.side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.side):
+            for i in range(reps):
+                fn(i)
+        return g
+
+    def time_replays(self, graph, reps, min_replays=MIN_REPLAYS, min_ms=MIN_TIMED_MS, max_replays=200):
+        """Replays `graph` (reps units each) back to back, each replay between its own pair of events on the launching
+        stream.  Returns (median, min) milliseconds per unit on this rank and the number of timed replays."""
+        torch = self.torch
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        graph.replay()                  # untimed: the first replay uploads the graph
+        torch.cuda.synchronize()
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        est = max(a.elapsed_time(b), 1e-3)
+        replays = int(min(max_replays, max(min_replays, math.ceil(min_ms / est))))
+        if self.world > 1:              # the same count on every rank
+            replays = int(self.max_over_ranks(float(replays)))
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+        self.barrier()
+        self.sampler.active.set()
+        evs[0].record()
+        for i in range(replays):
+            graph.replay()
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        self.sampler.active.clear()
+        self.barrier()
+        ms = sorted(evs[i].elapsed_time(evs[i + 1]) / reps for i in range(replays))
+        return ms[len(ms) // 2], ms[0], replays
+
+    def time_graph(self, fn, reps, **kw):
+        g = self.capture(fn, reps)
+        med, best, _ = self.time_replays(g, reps, **kw)
+        return self.max_over_ranks(med)
+
+
+def parity_case():
+    """One real packed layer (seeded codes and scales through the shipped packer) and its oracle result."""
+    from oracle import oracle as orc
+    m, n, k = M_DECODE, 4096, 4096
+    A, q, s = orc.make_problem(m, n, k, GROUP, seed=2024)
+    return (m, n, k), A, q, s, orc.c_gemm(A, q, s, GROUP)
+
+
+def run_ours(args):
+    ctx = Ctx()
+    torch, pkg, dev, world, rank, peaks = ctx.torch, ctx.pkg, ctx.dev, ctx.world, ctx.rank, ctx.peaks
+    warmup = max(args.warmup, 3)
+
+    layers = [ctx.make_layer(n, k, COPIES) for (n, k) in SHAPES]
+    acts = [ctx.randn_half(M_DECODE, k) for (_, k) in SHAPES]
     outs = [torch.zeros((M_DECODE, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
     wss = [torch.zeros(n // 128 * 16, dtype=torch.int, device=dev) for (n, _) in SHAPES]
 
@@ -197,284 +314,375 @@ def run_ours(args):
         for li in range(len(SHAPES)):
             pkg.mul(acts[li], layers[li][0][c], outs[li], layers[li][1][c], wss[li])
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    sampler = ClockSampler(local)
-    sampler.start()
-
-    # ---- warm-up (eager, on the stream the graph will be captured on)
-    side = torch.cuda.Stream(device=dev)
-    with torch.cuda.stream(side):
-        for i in range(max(args.warmup, 3)):
-            step(i)
-    side.synchronize()
-    pkg.device_status(local)
-
-    # ---- value: K steps captured in one CUDA graph, timed with events on the replay stream
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        for i in range(args.steps):
-            step(i)
-    graph.replay()               # untimed: first replay uploads the graph
-    barrier()
-    sampler.active.set()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    barrier()
-    ms_mine = e0.elapsed_time(e1)
-    ms_total = max_over_ranks(ms_mine)
-    ms_per_step = ms_total / args.steps
-    per_rank_ms = None
-    if world > 1:
-        t = torch.zeros(world, device=dev, dtype=torch.float64)
-        t[rank] = ms_mine / args.steps
-        dist.all_reduce(t)
-        per_rank_ms = [round(float(x), 5) for x in t.tolist()]
-    launches = args.steps * len(SHAPES)
+    # ---- value: K steps captured in one CUDA graph; >= 5 back-to-back replays, each timed with its own events
+    graph = ctx.capture(step, args.steps, warm=warmup)
+    pkg.device_status(ctx.local)
+    med_ms, min_ms, replays = ctx.time_replays(graph, args.steps)
+    ms_per_step = ctx.max_over_ranks(med_ms)
+    per_rank_med = ctx.per_rank(med_ms)
+    per_rank_min = ctx.per_rank(min_ms)
+    launches = args.steps * len(SHAPES) * replays
     wbytes = weight_bytes(SHAPES)
     value = world * wbytes / (ms_per_step * 1e-3) / 1e9
 
     alg = sum(algorithmic_bytes(M_DECODE, n, k) for n, k in SHAPES)
     achieved = alg / (ms_per_step * 1e-3) / 1e9     # per launch == per step here (same 4 launches / same time)
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                "kernel": "w4a16_tc_kernel<16,256,grouped>", "launch_us": ms_total * 1e3 / launches,
-                "algorithmic_bytes_per_launch": alg / len(SHAPES)}
-    roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH
-    roofline["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over the step's four launches (profiles/decode_m16_dram_traffic.md)"
+                "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": peaks["source"],
+                "kernel": "w4a16_decode_kernel<grouped> (tcgen05, m <= 16)", "launch_us": ms_per_step * 1e3 / len(SHAPES),
+                "algorithmic_bytes_per_launch": alg / len(SHAPES),
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over the step's four launches",
+                "replays": replays, "timed_region_ms": med_ms * args.steps * replays,
+                "per_rank_us_per_step_median": [round(v * 1e3, 3) for v in per_rank_med],
+                "per_rank_us_per_step_min": [round(v * 1e3, 3) for v in per_rank_min]}
+
+    # ---- parity of the timed call on a real packed layer (outside the timed regions)
+    from oracle import oracle as orc
+    (pm, pn, pk), pA, pq, ps, pref = parity_case()
+    pAt = torch.from_numpy(pA).to(dev)
+    pBt = torch.from_numpy(pkg.pack_weights(pq)).to(dev)
+    pst = torch.from_numpy(pkg.permute_scales(ps)).to(dev)
+    pC = torch.zeros((pm, pn), dtype=torch.half, device=dev)
+    pws = torch.zeros(pn // 128 * 16, dtype=torch.int, device=dev)
+    pkg.mul(pAt, pBt, pC, pst, pws)
+    pkg.device_status(ctx.local)
+    ok, err, bound = orc.tolerance_ok(pC.float().cpu().numpy(), pref)
+    roofline["max_err"], roofline["bound"], roofline["parity_ok"] = err, bound, bool(ok)
 
     # ---- e2e: the public call with host buffers, no graph
     hA = [a.cpu().pin_memory() for a in acts]
     hC = [torch.empty((M_DECODE, n), dtype=torch.half).pin_memory() for (n, _) in SHAPES]
-
-    # the step's four GEMMs are independent layers: each is issued on its own stream so that one layer's
-    # host<->device copies overlap another layer's kernel (each stream has its own library scratch)
     lanes = [torch.cuda.Stream(device=dev) for _ in SHAPES]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def e2e_step(i):
+    def e2e_step(i, streams):
         c = i % COPIES
         for li in range(len(SHAPES)):   # h2d copy of A, GEMM, d2h copy of C: one public call per GEMM
-            pkg.mul_host(hA[li], layers[li][0][c], hC[li], layers[li][1][c], wss[li], acts[li], outs[li], stream=lanes[li])
+            pkg.mul_host(hA[li], layers[li][0][c], hC[li], layers[li][1][c], wss[li], acts[li], outs[li], stream=streams[li])
 
-    for i in range(3):
-        e2e_step(i)
-    barrier()
-    e0.record()
-    for st_ in lanes:
-        st_.wait_event(e0)
-    for i in range(args.steps):
-        e2e_step(i)
-    for st_ in lanes:
-        torch.cuda.current_stream().wait_stream(st_)
-    e1.record()
-    torch.cuda.synchronize()
-    barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    def time_e2e(streams, steps):
+        for i in range(3):
+            e2e_step(i, streams)
+        ctx.barrier()
+        ctx.sampler.active.set()
+        e0.record()
+        for st_ in set(streams):
+            st_.wait_event(e0)
+        for i in range(steps):
+            e2e_step(i, streams)
+        for st_ in set(streams):
+            torch.cuda.current_stream().wait_stream(st_)
+        e1.record()
+        torch.cuda.synchronize()
+        ctx.sampler.active.clear()
+        ctx.barrier()
+        return ctx.max_over_ranks(e0.elapsed_time(e1)) / steps
+
+    e2e_steps = max(args.steps, int(MIN_TIMED_MS / 0.07))    # >= 50 ms of plain launches
+    e2e_ms = time_e2e(lanes, e2e_steps)
+    e2e_single_ms = time_e2e([lanes[0]] * len(SHAPES), e2e_steps)
     e2e = {"value": world * wbytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": sum(2 * M_DECODE * k for _, k in SHAPES),
-           "d2h_bytes_per_step": sum(2 * M_DECODE * n for n, _ in SHAPES), "ms_per_step": e2e_ms}
+           "d2h_bytes_per_step": sum(2 * M_DECODE * n for n, _ in SHAPES), "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "streams": "the step's four layers as independent requests, one stream each",
+           "value_single_stream": world * wbytes / (e2e_single_ms * 1e-3) / 1e9, "ms_per_step_single_stream": e2e_single_ms}
+    # parity of the host-buffer call
+    hpA = torch.from_numpy(pA).pin_memory()
+    hpC = torch.empty((pm, pn), dtype=torch.half).pin_memory()
+    pC.zero_()
+    pkg.mul_host(hpA, pBt, hpC, pst, pws, pAt, pC, stream=lanes[0])
+    lanes[0].synchronize()
+    pkg.device_status(ctx.local)
+    ok, err, bound = orc.tolerance_ok(hpC.float().numpy(), pref)
+    e2e["max_err"], e2e["bound"], e2e["parity_ok"] = err, bound, bool(ok)
 
-    # ---- extras: decode sweep and prefill (not the headline; same kernels, same timing method)
+    # ---- extras: decode sweep, prefill, large-K (not the headline; same kernels, same timing method)
     extras = {}
     if not args.no_extras:
-        def time_graph(fn, reps):
-            with torch.cuda.stream(side):
-                fn(0)
-            side.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                for i in range(reps):
-                    fn(i)
-            g.replay()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            g.replay()
-            b.record()
-            torch.cuda.synchronize()
-            return a.elapsed_time(b) / reps
-
         sweep = {}
         for m in (1, 2, 4, 8, 16, 32, 64):
-            am = [torch.randn((m, k), device=dev, generator=gen).half() for (_, k) in SHAPES]
+            am = [ctx.randn_half(m, k) for (_, k) in SHAPES]
             cm = [torch.zeros((m, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
-            per_shape = {}
-            for li, (n, k) in enumerate(SHAPES):
-                def one(i, li=li):
-                    c = i % COPIES
-                    pkg.mul(am[li], layers[li][0][c], cm[li], layers[li][1][c], wss[li])
-                # a single layer's 3 copies may fit in L2: pad the rotation with the other layers' traffic
-                ms = time_graph(one, 30)
-                per_shape["%dx%d" % (n, k)] = {"us": ms * 1e3, "weight_gbs": n * k / 2 / (ms * 1e-3) / 1e9}
+
             def allfour(i):
                 c = i % COPIES
                 for li in range(len(SHAPES)):
                     pkg.mul(am[li], layers[li][0][c], cm[li], layers[li][1][c], wss[li])
-            ms = time_graph(allfour, 20)
-            sweep["m%d" % m] = {"step_us": ms * 1e3, "weight_gbs": wbytes / (ms * 1e-3) / 1e9,
-                                "frac_of_peak": wbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "per_shape_l2_warmish": per_shape}
+            ms = ctx.time_graph(allfour, 20, min_ms=10.0)
+            sweep["m%d" % m] = {"step_us": round(ms * 1e3, 2), "weight_gbs": round(wbytes / (ms * 1e-3) / 1e9, 1),
+                                "frac_of_peak": round(wbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+            if m == M_DECODE:
+                per_shape = {}
+                for li, (n, k) in enumerate(SHAPES):
+                    def one(i, li=li):
+                        c = i % COPIES
+                        pkg.mul(am[li], layers[li][0][c], cm[li], layers[li][1][c], wss[li])
+                    # (a single layer's 3 copies may partly stay in L2: the figure is an upper bound for that shape)
+                    t = ctx.time_graph(one, 30, min_ms=10.0)
+                    per_shape["%dx%d" % (n, k)] = {"us": round(t * 1e3, 2), "weight_gbs": round(n * k / 2 / (t * 1e-3) / 1e9, 1)}
+                sweep["m%d" % m]["per_shape_l2_warmish"] = per_shape
         extras["decode_sweep"] = sweep
 
         prefill = {}
         for m in (1024, 4096):
-            am = [torch.randn((m, k), device=dev, generator=gen).half() for (_, k) in SHAPES]
+            am = [ctx.randn_half(m, k) for (_, k) in SHAPES]
             cm = [torch.zeros((m, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
             res = {}
             for li, (n, k) in enumerate(SHAPES):
                 def one(i, li=li):
                     pkg.mul(am[li], layers[li][0][i % COPIES], cm[li], layers[li][1][i % COPIES], wss[li])
-                ms = time_graph(one, 5)
+                ms = ctx.time_graph(one, 5, min_ms=20.0)
                 tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-                res["%dx%d" % (n, k)] = {"ms": ms, "tflops": tf, "frac_of_peak": tf / peaks["bf16_tflops"]}
+                res["%dx%d" % (n, k)] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_peak": round(tf / peaks["bf16_tflops"], 4)}
             tot_flops = sum(2.0 * m * n * k for n, k in SHAPES)
             tot_ms = sum(v["ms"] for v in res.values())
-            prefill["m%d" % m] = {"tflops": tot_flops / (tot_ms * 1e-3) / 1e12,
-                                  "frac_of_peak": tot_flops / (tot_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "per_shape": res}
+            prefill["m%d" % m] = {"tflops": round(tot_flops / (tot_ms * 1e-3) / 1e12, 1),
+                                  "frac_of_peak": round(tot_flops / (tot_ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4),
+                                  "frac_of_nominal_2250": round(tot_flops / (tot_ms * 1e-3) / 1e12 / 2250.0, 4), "per_shape": res}
             del am, cm
         extras["prefill"] = prefill
 
         # skinny batch, large K (N = 8192, K = 28672): every tile is cut between CTAs, so this is the stream-K split
         # and its fix-up; two resident weight copies (235 MB > L2) alternate
         sk_n, sk_k = 8192, 28672
-        skB, skS = make_layer(sk_n, sk_k, 2)
+        skB, skS = ctx.make_layer(sk_n, sk_k, 2)
         sk_ws = torch.zeros(sk_n // 128 * 16, dtype=torch.int, device=dev)
         streamk = {}
         for m in (16, 128):
-            a_sk = torch.randn((m, sk_k), device=dev, generator=gen).half()
+            a_sk = ctx.randn_half(m, sk_k)
             c_sk = torch.zeros((m, sk_n), dtype=torch.half, device=dev)
+
             def one(i):
                 pkg.mul(a_sk, skB[i % 2], c_sk, skS[i % 2], sk_ws)
-            ms = time_graph(one, 20)
+            ms = ctx.time_graph(one, 20, min_ms=10.0)
             t_hbm = algorithmic_bytes(m, sk_n, sk_k) / (peaks["hbm_gbs"] * 1e9)
             t_tensor = 2.0 * m * sk_n * sk_k / (peaks["bf16_tflops"] * 1e12)
-            streamk["m%d" % m] = {"us": ms * 1e3, "weight_gbs": sk_n * sk_k / 2 / (ms * 1e-3) / 1e9,
-                                  "tflops": 2.0 * m * sk_n * sk_k / (ms * 1e-3) / 1e12,
+            streamk["m%d" % m] = {"us": round(ms * 1e3, 2), "weight_gbs": round(sk_n * sk_k / 2 / (ms * 1e-3) / 1e9, 1),
+                                  "tflops": round(2.0 * m * sk_n * sk_k / (ms * 1e-3) / 1e12, 1),
                                   "roofline_bound": "hbm" if t_hbm >= t_tensor else "tensor",
-                                  "frac_of_roofline": max(t_hbm, t_tensor) / (ms * 1e-3)}
+                                  "frac_of_roofline": round(max(t_hbm, t_tensor) / (ms * 1e-3), 4)}
         del skB, skS
         extras["streamk_8192x28672"] = streamk
-        extras["peaks"] = peaks
 
     gathered = None
-    if world > 1:
-        # the step with the fp16 outputs all-gathered along N (only where a caller asks for the full row)
-        gbufs = [torch.empty((world * M_DECODE, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
+    if world > 1 and not args.no_extras:
+        gathered = measure_gathered_step(ctx, args, step, layers, acts, outs, wss)
 
-        def gstep(i):
-            step(i)
-            for li in range(len(SHAPES)):
-                dist.all_gather_into_tensor(gbufs[li], outs[li])
-        for i in range(3):
-            gstep(i)
-        barrier()
-        e0.record()
-        for i in range(args.steps):
-            gstep(i)
-        e1.record()
-        torch.cuda.synchronize()
-        barrier()
-        gms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
-        gathered = {"value": world * wbytes / (gms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": gms,
-                    "note": "eager launches + NCCL all_gather_into_tensor of the fp16 outputs per layer"}
-        # the same step with the gathering epilogue: the GEMM stores its tiles into every rank's output buffer over
-        # peer-mapped memory; a one-warp barrier kernel per layer takes the place of the collective
-        pbufs, why = None, ""
-        try:
-            pbufs = [pkg.GatherBuffers(M_DECODE, world * n, rank, world, dev) for (n, _) in SHAPES]
-        except Exception as exc:  # e.g. inter-process memory handles not permitted on this host
-            why = str(exc)[:200]
-        flag = torch.tensor([1 if pbufs is not None else 0], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)     # the arm runs on all ranks or on none
-        if int(flag.item()) == 0:
-            gathered["fused"] = {"unavailable": why or "a peer rank could not map the gather buffers"}
-            pbufs = None
-        try:
-            if pbufs is None:
-                raise StopIteration
+    # free the 7B layers before the 70B ones are made
+    del layers, graph
+    torch.cuda.empty_cache()
+    sharded = None
+    if not args.no_sharded:
+        sharded = measure_sharded70b(ctx)
 
-            def fstep(i):
-                c = i % COPIES
-                for li in range(len(SHAPES)):
-                    pkg.mul_gather(acts[li], layers[li][0][c], layers[li][1][c], wss[li], pbufs[li].dst_ptrs, rank)
-                    pbufs[li].barrier()
-            for i in range(3):
-                fstep(i)
-            barrier()
-            e0.record()
-            for i in range(args.steps):
-                fstep(i)
-            e1.record()
-            torch.cuda.synchronize()
-            barrier()
-            fms_eager = max_over_ranks(e0.elapsed_time(e1)) / args.steps
-            # and replayed from one CUDA graph, like `value` (the barrier's epoch counter lives on the device)
-            with torch.cuda.stream(side):
-                fstep(0)
-            side.synchronize()
-            fgraph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(fgraph, stream=side):
-                for i in range(args.steps):
-                    fstep(i)
-            fgraph.replay()
-            barrier()
-            e0.record()
-            fgraph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            barrier()
-            fms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
-            pkg.device_status(local)
-            same = all(torch.equal(pbufs[li].local[:, rank * n:(rank + 1) * n], outs[li]) for li, (n, _) in enumerate(SHAPES))
-            gathered["fused"] = {"value": world * wbytes / (fms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": fms,
-                                 "ms_per_step_eager": fms_eager, "own_columns_match_plain_gemm": bool(same),
-                                 "note": "K steps replayed from one CUDA graph; epilogue stores to all ranks' buffers + barrier kernel per layer, no NCCL"}
-        except StopIteration:
-            pass
-        except Exception as exc:
-            gathered["fused"] = {"unavailable": str(exc)[:200]}
-        if pbufs is not None:       # on every rank, whatever happened above: close() holds a collective
-            for b in pbufs:
-                b.close()
-
-    sampler.active.clear()
-    sampler.stop()
-    pkg.device_status(local)
-
+    pkg.device_status(ctx.local)
+    clocks = ctx.sampler.summary()
     if rank == 0:
         cpu_s, cpu_threads = cpu_time_step(reps=2) if world == 1 else (None, None)
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "l2": "weights rotate over %d resident copies (%.0f MB > 126 MB L2)"
-                       % (COPIES, COPIES * wbytes / 1e6), "launch": "K steps replayed from one CUDA graph",
-                       "parallelism": "column shards, one per GPU, no collective" if world > 1 else "single GPU"},
-            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
+            "dtype": "f16", "data": "synthetic", "config": CONFIG,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
         }
         if cpu_s is not None:
             line["cpu_baseline"] = {"value": wbytes / cpu_s / 1e9, "unit": UNIT, "cores": cpu_threads, "kind": "port",
                                     "sample": "one full step (4 GEMMs, M=16, 101 MB of packed weights), best of 2"}
+        line.update(extras)
         if gathered is not None:
             line["gathered"] = gathered
-        if per_rank_ms is not None:
-            line["per_rank_ms_per_step"] = per_rank_ms
-        line.update(extras)
+        line["peaks"] = peaks
+        if sharded is not None:
+            line["sharded70b"] = sharded      # last: the strong-scaling configuration, compact
         print(json.dumps(line), flush=True)
+    ctx.close()
+
+
+def measure_gathered_step(ctx, args, step, layers, acts, outs, wss):
+    """The weak-scaled decode step with the fp16 outputs all-gathered along N after every layer: NCCL, and the
+    GEMM's own gathering epilogue + barrier kernel."""
+    torch, dist, pkg, dev, world, rank = ctx.torch, ctx.dist, ctx.pkg, ctx.dev, ctx.world, ctx.rank
+    wbytes = weight_bytes(SHAPES)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gbufs = [torch.empty((world * M_DECODE, n), dtype=torch.half, device=dev) for (n, _) in SHAPES]
+    steps = max(args.steps, 100)
+
+    def gstep(i):
+        step(i)
+        for li in range(len(SHAPES)):
+            dist.all_gather_into_tensor(gbufs[li], outs[li])
+    for i in range(3):
+        gstep(i)
+    ctx.barrier()
+    e0.record()
+    for i in range(steps):
+        gstep(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ctx.barrier()
+    gms = ctx.max_over_ranks(e0.elapsed_time(e1)) / steps
+    gathered = {"value": world * wbytes / (gms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": gms,
+                "note": "eager launches + NCCL all_gather_into_tensor of the fp16 outputs per layer"}
+    pbufs, why = None, ""
+    try:
+        pbufs = [pkg.GatherBuffers(M_DECODE, world * n, rank, world, dev) for (n, _) in SHAPES]
+    except Exception as exc:  # e.g. inter-process memory handles not permitted on this host
+        why = str(exc)[:200]
+    flag = torch.tensor([1 if pbufs is not None else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)     # the arm runs on all ranks or on none
+    if int(flag.item()) == 0:
+        gathered["fused"] = {"unavailable": why or "a peer rank could not map the gather buffers"}
+        if pbufs is not None:
+            for b in pbufs:
+                b.close()
+        return gathered
+    try:
+        def fstep(i):
+            c = i % COPIES
+            for li in range(len(SHAPES)):
+                pkg.mul_gather(acts[li], layers[li][0][c], layers[li][1][c], wss[li], pbufs[li].dst_ptrs, rank)
+                pbufs[li].barrier()
+        fgraph = ctx.capture(fstep, args.steps, warm=3)
+        med, _, _ = ctx.time_replays(fgraph, args.steps)
+        fms = ctx.max_over_ranks(med)
+        pkg.device_status(ctx.local)
+        step(args.steps - 1)
+        torch.cuda.synchronize()
+        same = all(torch.equal(pbufs[li].local[:, rank * n:(rank + 1) * n], outs[li]) for li, (n, _) in enumerate(SHAPES))
+        gathered["fused"] = {"value": world * wbytes / (fms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": fms,
+                             "own_columns_match_plain_gemm": bool(same),
+                             "note": "graph replays; epilogue stores to all ranks' buffers + barrier kernel per layer, no NCCL"}
+    except Exception as exc:
+        gathered["fused"] = {"unavailable": str(exc)[:200]}
+    for b in pbufs:       # on every rank, whatever happened above: close() holds a collective
+        b.close()
+    return gathered
+
+
+def measure_sharded70b(ctx):
+    """The Llama-2-70B gate-up (57344 x 8192) and down (8192 x 28672) layers column-sharded over the ranks (strong
+    scaling: the layer is fixed, each rank owns N/G columns), M in {16, 4096}: GEMM alone; with N > 1 also + NCCL
+    all-gather of the fp16 outputs (graph) and the gathering epilogue + barrier kernel (graph).  Times are us per
+    GEMM, max over ranks of each rank's median replay.  On rank 0 a real packed shard is checked against the oracle."""
+    torch, dist, pkg, dev, world, rank, peaks = ctx.torch, ctx.dist, ctx.pkg, ctx.dev, ctx.world, ctx.rank, ctx.peaks
+    out = {}
+    for name, n_full, k in LAYERS70:
+        n = n_full // world
+        copies = 2 if n * k // 2 > 70e6 else 4
+        Bs, ss = ctx.make_layer(n, k, copies)
+        ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=dev)
+        for m in (16, 4096):
+            A = ctx.randn_half(m, k)
+            C = torch.zeros((m, n), dtype=torch.half, device=dev)
+            reps = 20 if m == 16 else 4
+
+            def one(i):
+                pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
+            ms = ctx.time_graph(one, reps, min_ms=20.0)
+            flops = 2.0 * m * n_full * k
+            wb = n_full * k / 2
+            res = {"us": round(ms * 1e3, 2), "tflops": round(flops / (ms * 1e-3) / 1e12, 1),
+                   "weight_gbs": round(wb / (ms * 1e-3) / 1e9, 1),
+                   "frac_hbm_per_gpu": round(algorithmic_bytes(m, n, k) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                   "frac_tensor_per_gpu": round(flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4)}
+            if world > 1:
+                try:  # + NCCL all-gather, replayed from a CUDA graph so that both arms are free of host launch cost
+                    def nccl_arm(i):
+                        one(i)
+                        pkg.all_gather_columns(C, world)
+                    res["nccl_gather_us"] = round(ctx.time_graph(nccl_arm, reps, min_ms=20.0) * 1e3, 2)
+                except Exception as exc:
+                    res["nccl_gather_unavailable"] = str(exc)[:120]
+                pb, why = None, "a peer rank could not map the gather buffers"
+                try:
+                    pb = pkg.GatherBuffers(m, n_full, rank, world, dev)
+                except Exception as exc:
+                    why = str(exc)[:200]
+                flag = torch.tensor([1 if pb is not None else 0], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)     # the arm runs on all ranks or on none
+                if int(flag.item()) == 1:
+                    try:
+                        def fused(i):
+                            pkg.mul_gather(A, Bs[i % copies], ss[i % copies], ws, pb.dst_ptrs, rank)
+                            pb.barrier()
+                        fms = ctx.time_graph(fused, reps, min_ms=20.0)
+                        pkg.device_status(ctx.local)
+                        # the last captured call used copy (reps - 1) % copies: the plain GEMM on it must give this
+                        # rank's columns of the gathered buffer bit for bit
+                        pkg.mul(A, Bs[(reps - 1) % copies], C, ss[(reps - 1) % copies], ws)
+                        torch.cuda.synchronize()
+                        res["fused_gather_us"] = round(fms * 1e3, 2)
+                        res["fused_own_columns_match"] = bool(torch.equal(pb.local[:, rank * n:(rank + 1) * n], C))
+                        # bytes this rank's epilogue sends to the other ranks, against the link rate
+                        res["fused_egress_gbs"] = round((world - 1) * 2.0 * m * n / (fms * 1e-3) / 1e9, 1)
+                    except Exception as exc:
+                        res["fused_gather_unavailable"] = str(exc)[:200]
+                    pb.close()     # on every rank, whatever happened above: close() holds a collective
+                else:
+                    res["fused_gather_unavailable"] = why
+                    if pb is not None:
+                        pb.close()
+            out["%s_m%d" % (name, m)] = res
+            del A, C
+        del Bs, ss
+        torch.cuda.empty_cache()
+    out["parity"] = sharded_parity(ctx)
+    tf = sum(2.0 * 4096 * nf * k for _, nf, k in LAYERS70) / sum(out["%s_m4096" % nm]["us"] * 1e-6 for nm, _, _ in LAYERS70) / 1e12
+    out["aggregate_tflops_m4096"] = round(tf, 1)
+    out["n_gpus"] = world
+    return out
+
+
+def sharded_parity(ctx):
+    """This rank's shard of a real packed down layer (8192 x 28672 cut with w4a16_shard_columns), M = 16, plain and
+    (N > 1) through the gathering epilogue, against the CPU oracle on two column windows.  Max over ranks."""
+    torch, dist, pkg, dev, world, rank = ctx.torch, ctx.dist, ctx.pkg, ctx.dev, ctx.world, ctx.rank
+    from oracle import oracle as orc
+    n_full, k, m = 8192, 28672, 16
+    n = n_full // world
+    A, q, s = orc.make_problem(m, n_full, k, GROUP, seed=70)      # the same on every rank
+    Bf, sf = pkg.pack_weights(q), pkg.permute_scales(s)
+    Br, sr = (Bf, sf) if world == 1 else pkg.shard_columns(Bf, sf, rank, world)
+    At, Bt, st = (torch.from_numpy(np.ascontiguousarray(x)).to(dev) for x in (A, Br, sr))
+    C = torch.zeros((m, n), dtype=torch.half, device=dev)
+    ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=dev)
+    pkg.mul(At, Bt, C, st, ws)
+    pkg.device_status(ctx.local)
+    res = {}
+
+    def worst(Cd, col0, width):
+        err_max, bound_min, ok_all = 0.0, float("inf"), True
+        for w0 in sorted(set([0, width - 256])):
+            g0 = col0 + w0
+            ref = orc.c_gemm(A, np.ascontiguousarray(q[:, g0:g0 + 256]), np.ascontiguousarray(s[:, g0:g0 + 256]), GROUP)
+            ok, err, bound = orc.tolerance_ok(Cd[:, w0:w0 + 256].float().cpu().numpy(), ref)
+            err_max, bound_min, ok_all = max(err_max, err), min(bound_min, bound), ok_all and ok
+        return err_max, bound_min, ok_all
+    err, bound, ok = worst(C, rank * n, n)
+    res["plain"] = {"max_err": ctx.max_over_ranks(err), "bound": bound, "ok": bool(ctx.max_over_ranks(0.0 if ok else 1.0) == 0.0)}
     if world > 1:
-        dist.destroy_process_group()
+        pb = None
+        try:
+            pb = pkg.GatherBuffers(m, n_full, rank, world, dev)
+        except Exception:
+            pb = None
+        flag = torch.tensor([1 if pb is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 1:
+            pkg.mul_gather(At, Bt, st, ws, pb.dst_ptrs, rank)
+            pb.barrier()
+            torch.cuda.synchronize()
+            pkg.device_status(ctx.local)
+            # the whole gathered row as this rank sees it: its own columns and every peer's
+            err, bound, ok = worst(pb.local, 0, n_full)
+            nxt = ((rank + 1) % world) * n
+            e2, b2, ok2 = worst(pb.local[:, nxt:nxt + n], nxt, n)
+            res["fused_gather"] = {"max_err": ctx.max_over_ranks(max(err, e2)), "bound": min(bound, b2),
+                                   "ok": bool(ctx.max_over_ranks(0.0 if (ok and ok2) else 1.0) == 0.0)}
+            pb.close()
+        elif pb is not None:
+            pb.close()
+    return res
 
 
 def run_case(args):
@@ -539,165 +747,17 @@ def run_case(args):
 
 
 def run_sharded70b(args):
-    """BASELINE.json configs[4]: Llama-2-70B layers column-sharded over the ranks (strong scaling: the layer is
-    fixed, each rank owns N/G columns), M in {16, 4096}, with and without the NCCL all-gather of the fp16 outputs.
-    One JSON line; `value` is the aggregate TFLOP/s at M = 4096 without the gather."""
-    import torch
-    import torch.distributed as dist
-
-    import __graft_entry__ as entry
-    pkg = entry.load_package()
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    peaks = load_peaks()
-    gen = torch.Generator(device=dev).manual_seed(99 + rank)
-    layers70 = [("gate_up", 57344, 8192), ("down", 8192, 28672)]
-    side = torch.cuda.Stream(device=dev)
-    out = {}
-    for name, n_full, k in layers70:
-        n = n_full // world
-        copies = 2 if n * k // 2 > 70e6 else 4
-        Bs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen) for _ in range(copies)]
-        ss = [(torch.rand((k // GROUP, n), device=dev, generator=gen) * 0.015 + 0.005).half() for _ in range(copies)]
-        ws = torch.zeros(n // 128 * 16, dtype=torch.int, device=dev)
-        for m in (16, 4096):
-            A = torch.randn((m, k), device=dev, generator=gen).half()
-            C = torch.zeros((m, n), dtype=torch.half, device=dev)
-            reps = 20 if m == 16 else 4
-
-            def one(i):
-                pkg.mul(A, Bs[i % copies], C, ss[i % copies], ws)
-            with torch.cuda.stream(side):
-                one(0)
-            side.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                for i in range(reps):
-                    one(i)
-            g.replay()
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            g.replay()
-            b.record()
-            torch.cuda.synchronize()
-            ms = a.elapsed_time(b) / reps
-            gms = None
-            if world > 1:
-                t = torch.tensor([ms], device=dev, dtype=torch.float64)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = float(t.item())
-                for _ in range(2):
-                    one(0)
-                    full = pkg.all_gather_columns(C, world)
-                torch.cuda.synchronize()
-                dist.barrier()
-                a.record()
-                for i in range(reps):
-                    one(i)
-                    full = pkg.all_gather_columns(C, world)
-                b.record()
-                torch.cuda.synchronize()
-                t = torch.tensor([a.elapsed_time(b) / reps], device=dev, dtype=torch.float64)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                gms = float(t.item())
-                del full
-                ggms = None
-                try:  # the NCCL variant replayed from a CUDA graph as well, so that both arms are free of host launch cost
-                    ng = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(ng, stream=side):
-                        for i in range(reps):
-                            one(i)
-                            full = pkg.all_gather_columns(C, world)
-                    ng.replay()
-                    torch.cuda.synchronize()
-                    dist.barrier()
-                    a.record()
-                    ng.replay()
-                    b.record()
-                    torch.cuda.synchronize()
-                    t = torch.tensor([a.elapsed_time(b) / reps], device=dev, dtype=torch.float64)
-                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                    ggms = float(t.item())
-                    del ng, full
-                except Exception:
-                    ggms = None
-                pb, why = None, "a peer rank could not map the gather buffers"
-                try:
-                    pb = pkg.GatherBuffers(m, n_full, rank, world, dev)
-                except Exception as exc:
-                    why = str(exc)[:200]
-                flag = torch.tensor([1 if pb is not None else 0], device=dev)
-                dist.all_reduce(flag, op=dist.ReduceOp.MIN)     # the arm runs on all ranks or on none
-                try:  # gathering epilogue + barrier kernel instead of the collective
-                    if int(flag.item()) == 0:
-                        raise RuntimeError(why)
-
-                    def fused(i):
-                        pkg.mul_gather(A, Bs[i % copies], ss[i % copies], ws, pb.dst_ptrs, rank)
-                        pb.barrier()
-                    with torch.cuda.stream(side):
-                        for i in range(2):
-                            fused(i)
-                    side.synchronize()
-                    fg = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(fg, stream=side):
-                        for i in range(reps):
-                            fused(i)
-                    fg.replay()
-                    torch.cuda.synchronize()
-                    dist.barrier()
-                    a.record()
-                    fg.replay()
-                    b.record()
-                    torch.cuda.synchronize()
-                    t = torch.tensor([a.elapsed_time(b) / reps], device=dev, dtype=torch.float64)
-                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                    fms = float(t.item())
-                    pkg.device_status(local)
-                    pkg.mul(A, Bs[(reps - 1) % copies], C, ss[(reps - 1) % copies], ws)
-                    torch.cuda.synchronize()
-                    fused_ok = bool(torch.equal(pb.local[:, rank * n:(rank + 1) * n], C))
-                except Exception as exc:
-                    fms, fused_ok = None, str(exc)[:200]
-                if int(flag.item()) == 1:   # on every rank, whatever happened above: close() holds a collective
-                    pb.close()
-            flops = 2.0 * m * n_full * k
-            wb = n_full * k / 2
-            res = {"us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12, "weight_gbs": wb / (ms * 1e-3) / 1e9,
-                   "frac_hbm_per_gpu": wb / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                   "frac_tensor_per_gpu": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
-            if gms is not None:
-                res["gathered_us"] = gms * 1e3
-                res["gathered_tflops"] = flops / (gms * 1e-3) / 1e12
-                if ggms is not None:
-                    res["gathered_graph_us"] = ggms * 1e3
-                if fms is not None:
-                    res["fused_gather_us"] = fms * 1e3
-                    res["fused_gather_tflops"] = flops / (fms * 1e-3) / 1e12
-                    res["fused_gather_own_columns_match"] = fused_ok
-                else:
-                    res["fused_gather_unavailable"] = fused_ok
-            out["%s_m%d" % (name, m)] = res
-            del A, C
-        del Bs, ss
-        torch.cuda.empty_cache()
-    pkg.device_status(local)
-    if rank == 0:
-        tf = sum(2.0 * 4096 * nf * k for _, nf, k in layers70) / sum(out["%s_m4096" % nm]["us"] * 1e-6 for nm, _, _ in layers70) / 1e12
-        print(json.dumps({"metric": "w4a16_llama70b_sharded_tflops_m4096", "value": tf, "unit": "TFLOP/s", "n_gpus": world,
-                          "higher_is_better": True, "scaling": "strong", "dtype": "f16", "data": "synthetic",
+    """Only the column-sharded Llama-2-70B configuration, as a line of its own."""
+    ctx = Ctx()
+    out = measure_sharded70b(ctx)
+    ctx.pkg.device_status(ctx.local)
+    if ctx.rank == 0:
+        print(json.dumps({"metric": "w4a16_llama70b_sharded_tflops_m4096", "value": out["aggregate_tflops_m4096"],
+                          "unit": "TFLOP/s", "n_gpus": ctx.world, "higher_is_better": True, "scaling": "strong",
+                          "dtype": "f16", "data": "synthetic",
                           "config": {"workload": "llama2-70b gate-up 57344x8192 and down 8192x28672, column-sharded, g128, M in {16,4096}"},
-                          "results": out, "peaks": peaks}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+                          "clocks": ctx.sampler.summary(), "results": out, "peaks": ctx.peaks}), flush=True)
+    ctx.close()
 
 
 def main():
@@ -706,18 +766,19 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-extras", action="store_true", help="skip the decode sweep and prefill extras")
+    ap.add_argument("--no-extras", action="store_true", help="skip the decode sweep, prefill and large-K extras")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the column-sharded 70B configuration")
     ap.add_argument("--case", default=None, help="NxKxM[xG]: time one shape only (graph replay; --eager for profilers)")
     ap.add_argument("--eager", action="store_true", help="with --case: plain launches instead of a CUDA graph")
     ap.add_argument("--workload", default="decode7b", choices=["decode7b", "sharded70b"],
-                    help="decode7b: the headline step; sharded70b: Llama-2-70B layers column-sharded over the ranks")
+                    help="decode7b: the headline step; sharded70b: only the Llama-2-70B layers column-sharded over the ranks")
     args = ap.parse_args()
-    if args.workload == "sharded70b":
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.workload == "sharded70b":
         run_sharded70b(args)
     elif args.case:
         run_case(args)
-    elif args.impl == "reference":
-        run_reference(args)
     else:
         run_ours(args)
 

@@ -44,7 +44,15 @@ extern "C" {
  *   max_par    kept for workspace sizing compatibility
  * Enqueues on `stream` and returns; 0 at once when m, n or k is 0 (marlin_cute_kernel.cu:59-60).
  * Scratch beyond the caller's workspace (fp32 partial tiles of the stream-K fix-up) is owned by the
- * library and cached per (device, stream); its first use on a (device, stream) calls cudaMalloc.
+ * library and cached per (device, stream), sized by need: the first use on a (device, stream) calls cudaMalloc
+ * for SMs x 64 x 128 fp32 (4.8 MB on a 148-SM B200), which covers every batch of up to 64 rows; batch tiles of
+ * 128 / 192 rows grow it once to at most SMs x 192 x 128 fp32 (14.5 MB).  Growing allocates, which CUDA refuses
+ * during stream capture: run a problem of each batch size once before capturing it.  A block that was outgrown
+ * stays allocated (captured launches may point at it) until w4a16_release_stream.
+ * Numerics: products are accumulated in fp32.  For m <= 16 with group scales the kernel accumulates the exact
+ * integer weights (q - 8) per 128-k group and applies the fp16 group scale in fp32 afterwards; the reference
+ * rounds (q - 8) * s to fp16 first (gemm/marlin_gemm/marlin_cute_trait.h:656-664), as this library does for larger m.
+ * The two differ by that rounding only (relative 2^-11 per weight).
  * Stream order holds for A, C, workspace and the scratch.  B and s are treated as parameters: when the
  * previous kernel on `stream` is another GEMM of this library, this one may prefetch B and s while that
  * one is still finishing (programmatic dependent launch), so B and s must not be that GEMM's output.
@@ -62,7 +70,7 @@ int w4a16_marlin_gemm(const void *A, const void *B, void *C, const void *s, int 
  * Who needs it: a process whose framework allocator has already reserved the whole device, so that a raw
  * cudaMalloc made by this library fails with out-of-memory or eats into memory the framework believes it
  * owns; a latency-critical loop, where cudaMalloc / cudaFree stall every stream of the device while they run;
- * and callers whose memory budget is audited, where a hidden per-stream cache of 17 MB is not acceptable.
+ * and callers whose memory budget is audited, where a library-owned cache of 5 to 15 MB per stream is not acceptable.
  * w4a16_marlin_gemm allocates its fix-up scratch on the first call of every (device, stream) pair; this entry
  * point never calls cudaMalloc, cudaFree or any allocating routine.  Its scratch is a 5 MiB array compiled
  * into the library (every GPU that loads the library holds it until the process exits).
@@ -71,8 +79,9 @@ int w4a16_marlin_gemm(const void *A, const void *B, void *C, const void *s, int 
  *   - prob_m <= 64 only, and at most 160 CTAs (any sm_100 part today); beyond that it returns W4A16_ERR_ARG and
  *     w4a16_last_cuda_error() says which limit was hit.  Larger batches must use w4a16_marlin_gemm.
  *   - The first call on a device looks up the device address of the built-in array (cudaGetSymbolAddress),
- *     puts the array into its idle state on `stream` and synchronises `stream`.  `dev` must be the current
- *     device.  Make that first call before any stream capture begins.
+ *     puts the array into its idle state on `stream` and synchronises `stream`.  Make that first call before
+ *     any stream capture begins.  On EVERY call `dev` must be the current device (checked: W4A16_ERR_ARG
+ *     otherwise), because the array's address on one device means nothing on another.
  *   - All calls on one device share the one array.  Each call leaves it in the idle state, so back-to-back
  *     calls on ONE stream are fine; two calls that overlap on the GPU (different streams, or different host
  *     threads feeding different streams) race on it and produce garbage.  Serialise them.
@@ -142,11 +151,17 @@ int w4a16_workspace_ints(int prob_n, int max_par);
  * (include/barrier.h:85-96). */
 int w4a16_device_status(int dev, void *stream);
 
+/* Frees the scratch and status word the library keeps for (dev, stream), after synchronising `stream`.  No launch
+ * captured in a CUDA graph on that stream may be replayed afterwards.  The reference has no counterpart (it owns
+ * no memory).  Returns W4A16_OK also when nothing was kept. */
+int w4a16_release_stream(int dev, void *stream);
+
 /* Self-test of the bounded device-side waits (the reference has none: its fix-up spin is unbounded,
  * include/barrier.h:85-96).  Launches the GEMM so that one CTA waits for a partial tile that no CTA will ever
  * write; after limit_ms (1..5000) the kernel gives up, unwinds and returns.  The call itself returns W4A16_OK;
  * w4a16_device_status(dev, stream) then returns W4A16_ERR_TIMEOUT and restores the scratch, after which the
- * stream is usable as before.  C is left undefined.  Injects no GPU fault. */
+ * stream is usable as before.  C is left undefined.  Injects no GPU fault.  A negative limit_ms runs the same on the
+ * built-in array of w4a16_marlin_gemm_builtin_scratch (prob_m <= 64) for -limit_ms milliseconds. */
 int w4a16_selftest_unanswered_wait(const void *A, const void *B, void *C, const void *s, int prob_m, int prob_n,
                                    int prob_k, int groupsize, int dev, void *stream, int limit_ms);
 

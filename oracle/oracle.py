@@ -241,6 +241,16 @@ def num_threads():
     return int(lib().oracle_num_threads())
 
 
+def use_all_cores():
+    """Run the C loops on every core this process may use, whatever OMP_NUM_THREADS the launcher exported."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().oracle_set_num_threads(ctypes.c_int(n))
+    return num_threads()
+
+
 # ----------------------------------------------------------------------------- seeded inputs
 def make_problem(m, n, k, groupsize, seed):
     """Synthetic operands with the distributions the benchmark configs name:

@@ -298,6 +298,17 @@ int oracle_gemm_packed(const uint16_t *A, const int32_t *B, const uint16_t *s_pa
   return rc;
 }
 
+/* Worker threads of the loops above.  A launcher may have exported OMP_NUM_THREADS=1 for its ranks (torchrun does);
+ * the CPU-baseline leg calls this with the host's core count so that it is timed on the same cores at every
+ * number of GPUs. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
