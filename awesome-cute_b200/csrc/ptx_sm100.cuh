@@ -248,6 +248,50 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// 4-byte relaxed store into the shared memory of any CTA of the cluster (address from map_to_cta), and the matching
+// load of the own shared memory: single-copy atomic, so a cell is seen either as it was or fully written
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.relaxed.cluster.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_relaxed_cluster(uint32_t cta_addr) {
+  uint32_t v;
+#ifdef W4A16_POLL_VOLATILE
+  asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(cta_addr) : "memory");
+#else
+  asm volatile("ld.relaxed.cluster.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(cta_addr) : "memory");
+#endif
+  return v;
+}
+// Arrive on a barrier of any CTA of the cluster, releasing this thread's earlier writes (to that CTA's shared memory
+// among others) at cluster scope; the waiter pairs it with mbar_wait_cluster.
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Bounded wait on a barrier of THIS CTA whose arrivals come from other CTAs of the cluster (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort, uint64_t limit_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((i & 0x3f) == 0) {
+      if (*abort) return false;
+      if (globaltimer_ns() - t0 > limit_ns) return false;
+    }
+  }
+}
+// The two halves of the cluster barrier: a thread that has arrived may do other work before it waits.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+// (relaxed: for when what the other CTAs need to see was already released, e.g. barrier initialisation by
+// fence.mbarrier_init.release.cluster)
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 // Every thread of every CTA of the cluster arrives and waits (hardware barrier, like __syncthreads for the cluster).
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");

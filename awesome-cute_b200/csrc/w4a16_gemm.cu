@@ -343,6 +343,97 @@ int launch_tc(const Problem &pr) {
   return launch_single<GeneralKernel<TM, KS, GROUPED, GATHER>>(pr);
 }
 
+// ---- m <= 16, few tiles: one cluster of CL CTAs per tile, partial tiles reduced over the cluster's shared memory
+// W4A16_CLUSTER=0 in the environment keeps these problems on the stream-K form (debugging aid, A/B timing)
+const bool g_use_cluster = [] {
+  const char *e = std::getenv("W4A16_CLUSTER");
+  return !(e && e[0] == '0');
+}();
+
+// Cluster size for a layer of n_tiles 128-column tiles and k_iters stages per tile: the one that fills most of the
+// SMs, if that is at least 0.6 of them and every rank gets between 2 and 32 stages; 0 = stay on stream-K.  (With
+// more stages per rank the problem is long enough for stream-K's use of every SM and its deeper ring to win:
+// 8192 x 28672 at m = 16 runs 26.6 us on stream-K, 27.3 us on 64 clusters of two.)
+int pick_cluster_size(int n_tiles, int k_iters, int nsm) {
+  int best = 0;
+  for (int cl = 2; cl <= 8; cl *= 2)
+    if (n_tiles * cl <= nsm && k_iters >= 2 * cl) best = cl;
+  if (!best || 10 * n_tiles * best < 6 * nsm || k_iters > 32 * best) return 0;
+  return best;
+}
+
+// Returns -2 when the clusters cannot all be resident at once on this device (the caller takes the stream-K form).
+template <bool GROUPED, int CL>
+int launch_decode_cluster(const Problem &pr) {
+  using Cfg = w4a16::DecodeConfig<false, CL>;
+  auto kern = w4a16::w4a16_decode_kernel<GROUPED, false, CL>;
+  constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
+  static bool attr_done[64] = {false};
+  static int max_clusters[64] = {0};
+
+  const int nsm = sm_count(pr.dev);
+  if (nsm <= 0) return W4A16_ERR_CUDA;
+  w4a16::Params p{};
+  p.m = pr.m, p.n = pr.n, p.k = pr.k;
+  p.n_tiles = pr.n / w4a16::TILE_N;
+  p.m_tiles = 1;
+  p.k_iters = pr.k / Cfg::KS;
+  p.total_iters = p.n_tiles * p.k_iters;
+  p.iters_per_cta = 1;                 // not used by the cluster form: rank r of a tile's cluster takes k_iters * [r, r + 1) / CL
+  p.s = static_cast<const __half *>(pr.s);
+  set_output(p, pr);
+  p.wait_ns = pr.wait_ns;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.n_tiles * CL));
+  cfg.blockDim = dim3((unsigned)Cfg::THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = pr.stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!attr_done[pr.dev]) {
+      if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"))
+        return W4A16_ERR_CUDA;
+      if (CL > 8 && !cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1), "cudaFuncSetAttribute"))
+        return W4A16_ERR_CUDA;
+      // rank 0 of a cluster waits for its other ranks, so the ranks must be co-resident: that is what a cluster
+      // guarantees; clusters beyond the resident ones simply run later
+      cudaLaunchConfig_t probe = cfg;
+      probe.gridDim = dim3((unsigned)(nsm / CL * CL));
+      int clusters = 0;
+      if (!cuda_ok(cudaOccupancyMaxActiveClusters(&clusters, kern, &probe), "cudaOccupancyMaxActiveClusters")) return W4A16_ERR_CUDA;
+      max_clusters[pr.dev] = clusters;
+      attr_done[pr.dev] = true;
+    }
+  }
+  if (max_clusters[pr.dev] < p.n_tiles) return -2;   // a second wave of clusters would double the time: stream-K instead
+  Maps mp;
+  if (!get_maps(pr, Cfg::KS, Cfg::TM, GROUPED, mp)) return W4A16_ERR_CUDA;
+  p.a_box3d = mp.a_box3d;
+  if (!get_scratch(pr, 0, p)) return W4A16_ERR_CUDA;   // the status word only: the partial tiles never leave the cluster
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, p), "kernel launch (clusters)")) return W4A16_ERR_CUDA;
+  return W4A16_OK;
+}
+
+int launch_decode_cluster_g(const Problem &pr, int cl) {
+  const bool g = pr.groupsize == 128;
+  switch (cl) {
+    case 2: return g ? launch_decode_cluster<true, 2>(pr) : launch_decode_cluster<false, 2>(pr);
+    case 4: return g ? launch_decode_cluster<true, 4>(pr) : launch_decode_cluster<false, 4>(pr);
+    case 8: return g ? launch_decode_cluster<true, 8>(pr) : launch_decode_cluster<false, 8>(pr);
+  }
+  return -2;
+}
+
 // ---- large batches on CTA pairs (cta_group::2): see w4a16_kernel_2sm.cuh
 // W4A16_WAVES=0 in the environment keeps the CTA-pair kernel on contiguous stream-K ranges only (debugging aid)
 const bool g_use_waves = [] {
@@ -489,7 +580,17 @@ int launch_decode_g(const Problem &pr) {
 int dispatch_tc(const Problem &pr) {
   // batch tile = UMMA N; the k per stage is as deep as the activation tile allows (fewer, larger TMAs)
   const bool k256 = (pr.k % 256) == 0, k128 = (pr.k % 128) == 0;
-  if (pr.m <= 16 && k256 && g_use_decode) return launch_decode_g(pr);   // the HBM-bound case has a kernel of its own
+  if (pr.m <= 16 && k256 && g_use_decode) {   // the HBM-bound case has a kernel of its own
+    // few tiles and no split count from the caller: one cluster per tile
+    if (g_use_cluster && pr.sms <= 0 && pr.c_ld == 0 && !pr.orphan_finisher) {
+      const int cl = pick_cluster_size(pr.n / w4a16::TILE_N, pr.k / 256, sm_count(pr.dev));
+      if (cl) {
+        const int rc = launch_decode_cluster_g(pr, cl);
+        if (rc != -2) return rc;
+      }
+    }
+    return launch_decode_g(pr);
+  }
   if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
   // 17..32 rows on CTA pairs as well (+12-16 %)
   if (g_use_pairs && pr.m > 16 && pr.m <= 32 && k256 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {

@@ -34,8 +34,10 @@
 
 namespace w4a16 {
 
-template <bool GATHER = false>
+template <bool GATHER = false, int CL = 1>
 struct DecodeConfig {
+  static_assert(CL == 1 || CL == 2 || CL == 4 || CL == 8, "cluster size along k");
+  static_assert(CL == 1 || !GATHER, "the gathering epilogue runs on the stream-K form");
   static constexpr int TM = 16;                              // batch tile = UMMA N
   static constexpr int KS = 256;                             // k per stage
   static constexpr int KCHUNKS = KS / 64;
@@ -58,10 +60,15 @@ struct DecodeConfig {
   static constexpr int THREADS = (NDQ + EPI_WARPS + 1 + NMMA) * 32;
   static constexpr int BAR_BYTES = 1024;
   static constexpr int GATHER_BYTES = GATHER ? GATHER_SLAB_BYTES : 0;
+  // cluster form: the other ranks' fp32 partial tiles land here, in rank 0's shared memory: [CL - 1][TM][128] fp32
+  static constexpr int XSLAB_BYTES = (CL - 1) * TM * TILE_N * 4;
   static constexpr int SMEM_MAX = 227 * 1024;
-  static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - GATHER_BYTES - 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + GATHER_BYTES + 1024 /*align slack*/;
+  static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - GATHER_BYTES - XSLAB_BYTES - 1024) / STAGE_BYTES;
+  // a multiple of the number of dequant sets, so that a stage is always converted by the same set; in the cluster
+  // form a CTA runs few stages and six are plenty
+  static constexpr int STAGES = CL > 1 ? 6 : (STAGES_RAW > 12 ? 12 : STAGES_RAW);
+  static_assert(STAGES <= STAGES_RAW, "shared memory budget");
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + GATHER_BYTES + XSLAB_BYTES + 1024 /*align slack*/;
 };
 
 struct DecodeBars {  // lives in shared memory
@@ -91,6 +98,12 @@ __device__ __noinline__ bool fold_partial_slices(uint32_t (&v)[16], uint32_t *pa
     for (int f = 0; f < FLY; ++f) src[f] = partials + ((size_t)min(c + f, last) * rows + c0) * TILE_N + row;
     uint32_t x[FLY][16];
     for (uint32_t spin = 0;; ++spin) {
+#ifdef W4A16_TRACE
+      if (g_trace && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 12) {
+        g_trace[4096 + blockIdx.x * 16 + 12] = spin + 1;                                   // poll rounds
+        if (spin == 1 && c == first) g_trace[blockIdx.x * 16 + 14] = globaltimer_ns();     // first poll came back
+      }
+#endif
       bool up = true;
 #pragma unroll
       for (int f = 0; f < FLY; ++f)
@@ -117,11 +130,16 @@ __device__ __noinline__ bool fold_partial_slices(uint32_t (&v)[16], uint32_t *pa
   return true;
 }
 
-template <bool GROUPED, bool GATHER = false>
+// CL > 1: the cluster form for layers with few tiles.  A cluster of CL CTAs (launched with that cluster dimension) owns
+// one tile and cuts its k-range CL ways; ranks 1.. send their fp32 partial tile straight into rank 0's shared memory
+// (st.shared::cluster; the data is its own flag, as in the stream-K fix-up), and rank 0 adds them in rank order and writes C.  The stream-K
+// form's fix-up goes through L2 instead, and when all CTAs of a tile finish together (which they do when a tile is cut
+// evenly) that costs the finisher two L2 round trips after everybody else is done; inside a cluster it is one hop.
+template <bool GROUPED, bool GATHER = false, int CL = 1>
 __global__ void __launch_bounds__(DecodeConfig<>::THREADS, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ CUtensorMap tmS, const Params p) {
-  using Cfg = DecodeConfig<GATHER>;
+  using Cfg = DecodeConfig<GATHER, CL>;
   using namespace sm100;
   constexpr int S = Cfg::STAGES, NDQ = Cfg::NDQ, TM = Cfg::TM, KS = Cfg::KS;
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;   // first of NMMA issuer warps
@@ -139,9 +157,19 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
   const int lane = threadIdx.x & 31;
   if (warp == 0) W4A16_STAMP(0);   // kernel entry
 
-  // this CTA's slice of the linearised (tile, k-stage) space
-  const int it_begin = min(p.total_iters, (int)blockIdx.x * p.iters_per_cta);
-  const int it_end = min(p.total_iters, it_begin + p.iters_per_cta);
+  // this CTA's slice of the linearised (tile, k-stage) space: an equal contiguous range (stream-K), or in the cluster
+  // form the rank's share of the cluster's tile
+  int it_begin, it_end;
+  uint32_t crank = 0;
+  if constexpr (CL > 1) {
+    crank = cluster_ctarank();
+    const int tile = (int)blockIdx.x / CL;
+    it_begin = tile * p.k_iters + (p.k_iters * (int)crank) / CL;
+    it_end = tile * p.k_iters + (p.k_iters * ((int)crank + 1)) / CL;
+  } else {
+    it_begin = min(p.total_iters, (int)blockIdx.x * p.iters_per_cta);
+    it_end = min(p.total_iters, it_begin + p.iters_per_cta);
+  }
   const int nsteps = it_end - it_begin;
 
   auto issue_weights = [&](int st, int n_idx, int kk) {   // packed weights + group scales: immutable parameters
@@ -229,6 +257,23 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Cluster form: rank 0's slab must hold the idle pattern before another rank writes into it.  Every thread arrives
+  // at the cluster barrier here and waits for it only where it needs the guarantee (the epilogue threads of ranks 1..
+  // right before they send, everybody else at the end): waiting here held every warp for about a microsecond.
+  bool cluster_waited = false;
+  if (warp == 0) W4A16_STAMP(15);  // CTA-wide sync passed
+  if constexpr (CL > 1) {
+    if (crank == 0 && warp >= NDQ && warp < NDQ + EPI_WARPS) {
+      // rank 0's epilogue warps, idle for the next microseconds, put the idle pattern into the slab; their arrive
+      // releases it at cluster scope (that release is what costs ~1500 clocks: nobody else pays it)
+      uint32_t *cell = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES) + (warp - NDQ) * 32 + lane;
+#pragma unroll 4
+      for (int i = 0; i < (CL - 1) * TM; ++i) cell[(size_t)i * TILE_N] = PARTIAL_IDLE;
+      cluster_arrive();
+    } else {
+      cluster_arrive_relaxed();
+    }
+  }
   if (warp == 0) W4A16_STAMP(1);   // prologue done
   const uint32_t tmem = __shfl_sync(0xffffffffu, bars->tmem_base, 0);  // provably warp-uniform
 
@@ -315,6 +360,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     const uint32_t sS_u = smem_u32(sS);
     pdl_wait_prior_grid();   // C and the partial-tile scratch may still be in use by the previous kernel
     __half *slabs = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES);   // gathering form only
+    float *xslab = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES);     // cluster form only
     int gcount = 0;
     int step = 0;
     bool ok = true;
@@ -375,13 +421,42 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       uint32_t v[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(f[i]);
-      if (!finisher) {
+      if (CL > 1 && !finisher) {
+        // cluster form, ranks 1..: the partial tile goes into rank 0's slab [rank - 1][16][128], one hop over the
+        // cluster's shared-memory network.  As in the stream-K form the data is its own flag (a cell is written when
+        // it no longer holds the idle pattern): a release at cluster scope would cost the sender ~1500 clocks.
+        const uint32_t dst = map_to_cta(smem_u32(xslab + ((size_t)(crank - 1) * TM) * TILE_N + row), 0);
+        if (!cluster_waited) { cluster_wait(); cluster_waited = true; }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) st_shared_cluster_u32(dst + (uint32_t)i * TILE_N * 4, v[i] == PARTIAL_IDLE ? 0x7fffffffu : v[i]);
+      } else if (!finisher) {
         // the data is its own flag: anything but the idle pattern means "written"
         uint32_t *part = p.partials + ((size_t)blockIdx.x * TM) * TILE_N + row;
 #pragma unroll
         for (int i = 0; i < 16; ++i) st_slot(part + (size_t)i * TILE_N, v[i] == PARTIAL_IDLE ? 0x7fffffffu : v[i]);
       } else {
-        if (ncontrib > 0) {
+        if constexpr (CL > 1) {
+          // rank 0: re-read its own slab until no cell shows the idle pattern, then add in rank order
+          const uint32_t cell0 = smem_u32(xslab) + (uint32_t)row * 4;
+          const uint64_t t0 = globaltimer_ns();
+          for (uint32_t spin = 0;; ++spin) {
+            bool up = true;
+#pragma unroll 1
+            for (int r = 0; r < CL - 1; ++r)
+#pragma unroll
+              for (int i = 0; i < TM; ++i) up &= (ld_shared_relaxed_cluster(cell0 + (uint32_t)((r * TM + i) * TILE_N * 4)) != PARTIAL_IDLE);
+            if (__all_sync(0xffffffffu, up)) break;
+            if ((spin & 0x3f) == 0x3f && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > p.wait_ns)) { ok = false; break; }
+          }
+          if (!ok) { give_up(p, abort, 4); break; }
+#pragma unroll 1
+          for (int r = 0; r < CL - 1; ++r)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) f[i] += __uint_as_float(ld_shared_relaxed_cluster(cell0 + (uint32_t)((r * TM + i) * TILE_N * 4)));
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(f[i]);
+          if (warp == NDQ) W4A16_STAMP(7);             // partial tiles folded in
+        } else if (ncontrib > 0) {
           const uint64_t t0 = globaltimer_ns();
           if (!fold_partial_slices<3>(v, p.partials, TM, 0, row, (int)blockIdx.x + 1, last_contrib, abort, t0, p.wait_ns)) {
             give_up(p, abort, 4);
@@ -501,6 +576,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);
     W4A16_STAMP(13);                       // TMEM freed
+  }
+  // cluster form: rank 0's shared memory must outlive every store the other ranks may still send into it (they send
+  // only on the regular path, microseconds before this point; after a time-out nobody sends)
+  if constexpr (CL > 1) {
+    if (!cluster_waited) cluster_wait();
+    cluster_sync_all();
   }
 }
 
