@@ -90,6 +90,20 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, 
       : "memory");
 }
 
+// Stores: shared memory -> global through a tensor map (rows and columns outside the tensor are clipped).  The bytes
+// must have been made visible to the async proxy (fence_proxy_async_smem by every writer, then a barrier) before one
+// thread issues the copy; that thread owns the bulk group and is the one that waits on it.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, int c0, int c1, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(m), "r"(c0), "r"(c1), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's bulk groups have finished READING shared memory (the source may be overwritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... have completed (the global writes are done)
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------ tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
@@ -255,36 +269,8 @@ __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uin
 }
 __device__ __forceinline__ uint32_t ld_shared_relaxed_cluster(uint32_t cta_addr) {
   uint32_t v;
-#ifdef W4A16_POLL_VOLATILE
-  asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(cta_addr) : "memory");
-#else
   asm volatile("ld.relaxed.cluster.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(cta_addr) : "memory");
-#endif
   return v;
-}
-// Arrive on a barrier of any CTA of the cluster, releasing this thread's earlier writes (to that CTA's shared memory
-// among others) at cluster scope; the waiter pairs it with mbar_wait_cluster.
-__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// Bounded wait on a barrier of THIS CTA whose arrivals come from other CTAs of the cluster (acquire at cluster scope).
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort, uint64_t limit_ns) {
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t i = 1;; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((i & 0x3f) == 0) {
-      if (*abort) return false;
-      if (globaltimer_ns() - t0 > limit_ns) return false;
-    }
-  }
 }
 // The two halves of the cluster barrier: a thread that has arrived may do other work before it waits.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }

@@ -177,19 +177,19 @@ void set_output(w4a16::Params &p, const Problem &pr) {
 // ---- tensor maps.  They depend only on the operands' addresses, the shape and the kernel's box sizes, and encoding
 // them is most of a launch's host time, so they are kept: key (B, A, s, m, n, k, k per stage, activation rows per box).
 struct Maps {
-  CUtensorMap b, a, s;
+  CUtensorMap b, a, s, c;
   int a_box3d;
 };
 struct MapKey {
-  const void *B, *A, *s;
+  const void *B, *A, *s, *C;   // C only for the TMA-store epilogue (else null: the maps do not depend on it)
   int m, n, k, ks, a_rows, grouped;
   bool operator<(const MapKey &o) const {
-    return std::tie(B, A, s, m, n, k, ks, a_rows, grouped) < std::tie(o.B, o.A, o.s, o.m, o.n, o.k, o.ks, o.a_rows, o.grouped);
+    return std::tie(B, A, s, C, m, n, k, ks, a_rows, grouped) < std::tie(o.B, o.A, o.s, o.C, o.m, o.n, o.k, o.ks, o.a_rows, o.grouped);
   }
 };
 std::map<MapKey, Maps> g_maps;   // guarded by g_mu
 
-bool build_maps(const Problem &pr, int ks, int a_rows, bool grouped, Maps &mp) {
+bool build_maps(const Problem &pr, int ks, int a_rows, bool grouped, bool tma_store, Maps &mp) {
   {  // weights: int32 [k/16][2n] viewed as [k/16][2n/32][32] so a 128-byte inner box can be swizzled
     const cuuint64_t dims[3] = {32, (cuuint64_t)(2 * pr.n / 32), (cuuint64_t)(pr.k / 16)};
     const cuuint64_t strides[2] = {128, (cuuint64_t)pr.n * 8};
@@ -222,18 +222,27 @@ bool build_maps(const Problem &pr, int ks, int a_rows, bool grouped, Maps &mp) {
   } else {
     mp.s = mp.a;  // never read
   }
+  if (tma_store) {  // output: fp16 [m][n]; the epilogue stores boxes of 16 rows x 128 columns, rows past m are clipped
+    const cuuint64_t dims[2] = {(cuuint64_t)pr.n, (cuuint64_t)pr.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)pr.n * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)w4a16::TILE_N, 16};
+    if (!encode(&mp.c, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pr.C, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "C"))
+      return false;
+  } else {
+    mp.c = mp.a;  // never read
+  }
   return true;
 }
 
 // Takes g_mu for the lookup only.
-bool get_maps(const Problem &pr, int ks, int a_rows, bool grouped, Maps &out) {
-  if (pr.fixed_partials) return build_maps(pr, ks, a_rows, grouped, out);  // the allocation-free entry point keeps nothing, on the host either
-  const MapKey key{pr.B, pr.A, pr.s, pr.m, pr.n, pr.k, ks, a_rows, grouped ? 1 : 0};
+bool get_maps(const Problem &pr, int ks, int a_rows, bool grouped, bool tma_store, Maps &out) {
+  if (pr.fixed_partials) return build_maps(pr, ks, a_rows, grouped, tma_store, out);  // the allocation-free entry point keeps nothing, on the host either
+  const MapKey key{pr.B, pr.A, pr.s, tma_store ? pr.C : nullptr, pr.m, pr.n, pr.k, ks, a_rows, grouped ? 1 : 0};
   std::lock_guard<std::mutex> lock(g_mu);
   auto it = g_maps.find(key);
   if (it == g_maps.end()) {
     Maps mp;
-    if (!build_maps(pr, ks, a_rows, grouped, mp)) return false;
+    if (!build_maps(pr, ks, a_rows, grouped, tma_store, mp)) return false;
     if (g_maps.size() >= 1024) g_maps.clear();
     it = g_maps.emplace(key, mp).first;
   }
@@ -262,19 +271,19 @@ bool get_scratch(const Problem &pr, size_t need_slots, w4a16::Params &p) {
 }
 
 // the kernels behind launch_single, as traits
-template <int TM_, int KS_, bool GROUPED_, bool GATHER_>
+template <int TM_, int KS_, bool GROUPED_, int OUT_>
 struct GeneralKernel {
-  using Cfg = w4a16::Config<TM_, KS_, GATHER_>;
-  static constexpr int TM = TM_, KS = KS_, THREADS = Cfg::THREADS, SMEM = Cfg::SMEM_BYTES;
+  using Cfg = w4a16::Config<TM_, KS_, OUT_>;
+  static constexpr int TM = TM_, KS = KS_, THREADS = Cfg::THREADS, SMEM = Cfg::SMEM_BYTES, OUT = OUT_;
   static constexpr bool GROUPED = GROUPED_;
-  static auto kernel() { return w4a16::w4a16_tc_kernel<TM_, KS_, GROUPED_, GATHER_>; }
+  static auto kernel() { return w4a16::w4a16_tc_kernel<TM_, KS_, GROUPED_, OUT_>; }
 };
-template <bool GROUPED_, bool GATHER_>
+template <bool GROUPED_, int OUT_>
 struct DecodeKernel {
-  using Cfg = w4a16::DecodeConfig<GATHER_>;
-  static constexpr int TM = Cfg::TM, KS = Cfg::KS, THREADS = Cfg::THREADS, SMEM = Cfg::SMEM_BYTES;
+  using Cfg = w4a16::DecodeConfig<OUT_>;
+  static constexpr int TM = Cfg::TM, KS = Cfg::KS, THREADS = Cfg::THREADS, SMEM = Cfg::SMEM_BYTES, OUT = OUT_;
   static constexpr bool GROUPED = GROUPED_;
-  static auto kernel() { return w4a16::w4a16_decode_kernel<GROUPED_, GATHER_>; }
+  static auto kernel() { return w4a16::w4a16_decode_kernel<GROUPED_, OUT_>; }
 };
 
 // One CTA per SM, persistent, stream-K over (128-column tile, k-stage).
@@ -312,7 +321,7 @@ int launch_single(const Problem &pr) {
   }
 
   Maps mp;
-  if (!get_maps(pr, K::KS, K::TM, K::GROUPED, mp)) return W4A16_ERR_CUDA;
+  if (!get_maps(pr, K::KS, K::TM, K::GROUPED, K::OUT == w4a16::OUT_TMA, mp)) return W4A16_ERR_CUDA;
   p.a_box3d = mp.a_box3d;
   if (!get_scratch(pr, (size_t)grid * K::TM * w4a16::TILE_N, p)) return pr.fixed_partials ? W4A16_ERR_ARG : W4A16_ERR_CUDA;
   if (!attr_done[pr.dev]) {   // (idempotent: a race between two host threads sets the same value twice)
@@ -334,13 +343,13 @@ int launch_single(const Problem &pr) {
   attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, p), "kernel launch")) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, mp.c, p), "kernel launch")) return W4A16_ERR_CUDA;
   return W4A16_OK;
 }
 
-template <int TM, int KS, bool GROUPED, bool GATHER>
+template <int TM, int KS, bool GROUPED, int OUT>
 int launch_tc(const Problem &pr) {
-  return launch_single<GeneralKernel<TM, KS, GROUPED, GATHER>>(pr);
+  return launch_single<GeneralKernel<TM, KS, GROUPED, OUT>>(pr);
 }
 
 // ---- m <= 16, few tiles: one cluster of CL CTAs per tile, partial tiles reduced over the cluster's shared memory
@@ -363,10 +372,10 @@ int pick_cluster_size(int n_tiles, int k_iters, int nsm) {
 }
 
 // Returns -2 when the clusters cannot all be resident at once on this device (the caller takes the stream-K form).
-template <bool GROUPED, int CL>
+template <bool GROUPED, int OUT, int CL>
 int launch_decode_cluster(const Problem &pr) {
-  using Cfg = w4a16::DecodeConfig<false, CL>;
-  auto kern = w4a16::w4a16_decode_kernel<GROUPED, false, CL>;
+  using Cfg = w4a16::DecodeConfig<OUT, CL>;
+  auto kern = w4a16::w4a16_decode_kernel<GROUPED, OUT, CL>;
   constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
   static bool attr_done[64] = {false};
   static int max_clusters[64] = {0};
@@ -417,21 +426,38 @@ int launch_decode_cluster(const Problem &pr) {
   }
   if (max_clusters[pr.dev] < p.n_tiles) return -2;   // a second wave of clusters would double the time: stream-K instead
   Maps mp;
-  if (!get_maps(pr, Cfg::KS, Cfg::TM, GROUPED, mp)) return W4A16_ERR_CUDA;
+  if (!get_maps(pr, Cfg::KS, Cfg::TM, GROUPED, OUT == w4a16::OUT_TMA, mp)) return W4A16_ERR_CUDA;
   p.a_box3d = mp.a_box3d;
   if (!get_scratch(pr, 0, p)) return W4A16_ERR_CUDA;   // the status word only: the partial tiles never leave the cluster
-  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, p), "kernel launch (clusters)")) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, mp.c, p), "kernel launch (clusters)")) return W4A16_ERR_CUDA;
   return W4A16_OK;
 }
 
-int launch_decode_cluster_g(const Problem &pr, int cl) {
+// W4A16_TMA_STORE=0 / 1 in the environment picks how finished tiles of the plain GEMM reach C: 2-byte stores from
+// registers, or staged in shared memory and stored by the copy engine (cp.async.bulk.tensor).  Both are compiled
+// and tested; the default is the one measured faster (see tma_store_default).
+const int g_tma_store = [] {
+  const char *e = std::getenv("W4A16_TMA_STORE");
+  return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1;
+}();
+bool tma_store_default(const Problem &pr) {
+  (void)pr;
+  return false;
+}
+bool use_tma_store(const Problem &pr) { return g_tma_store >= 0 ? g_tma_store == 1 : tma_store_default(pr); }
+
+template <int OUT>
+int launch_decode_cluster_o(const Problem &pr, int cl) {
   const bool g = pr.groupsize == 128;
   switch (cl) {
-    case 2: return g ? launch_decode_cluster<true, 2>(pr) : launch_decode_cluster<false, 2>(pr);
-    case 4: return g ? launch_decode_cluster<true, 4>(pr) : launch_decode_cluster<false, 4>(pr);
-    case 8: return g ? launch_decode_cluster<true, 8>(pr) : launch_decode_cluster<false, 8>(pr);
+    case 2: return g ? launch_decode_cluster<true, OUT, 2>(pr) : launch_decode_cluster<false, OUT, 2>(pr);
+    case 4: return g ? launch_decode_cluster<true, OUT, 4>(pr) : launch_decode_cluster<false, OUT, 4>(pr);
+    case 8: return g ? launch_decode_cluster<true, OUT, 8>(pr) : launch_decode_cluster<false, OUT, 8>(pr);
   }
   return -2;
+}
+int launch_decode_cluster_g(const Problem &pr, int cl) {
+  return use_tma_store(pr) ? launch_decode_cluster_o<w4a16::OUT_TMA>(pr, cl) : launch_decode_cluster_o<w4a16::OUT_PLAIN>(pr, cl);
 }
 
 // ---- large batches on CTA pairs (cta_group::2): see w4a16_kernel_2sm.cuh
@@ -464,10 +490,10 @@ int pick_tile_order(int dev, double act_bytes, double weight_bytes, int n_tiles,
   return m_first < 0.9 * n_first ? 1 : 0;
 }
 
-template <int TM, int KS, bool GROUPED, bool GATHER>
+template <int TM, int KS, bool GROUPED, int OUT>
 int launch_tc2(const Problem &pr) {
-  using Cfg = w4a16::Config2<TM, KS, GATHER>;
-  auto kern = w4a16::w4a16_tc2_kernel<TM, KS, GROUPED, GATHER>;
+  using Cfg = w4a16::Config2<TM, KS, OUT>;
+  auto kern = w4a16::w4a16_tc2_kernel<TM, KS, GROUPED, OUT>;
   constexpr int smem = Cfg::SMEM_BYTES > 116 * 1024 ? Cfg::SMEM_BYTES : 116 * 1024;
   static bool attr_done[64] = {false};
   static int max_pairs[64] = {0};
@@ -535,13 +561,13 @@ int launch_tc2(const Problem &pr) {
   p.workers = pairs;
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   Maps mp;   // each CTA of the pair loads half of the tile's activation rows
-  if (!get_maps(pr, Cfg::KS, Cfg::HALF_ROWS, GROUPED, mp)) return W4A16_ERR_CUDA;
+  if (!get_maps(pr, Cfg::KS, Cfg::HALF_ROWS, GROUPED, OUT == w4a16::OUT_TMA, mp)) return W4A16_ERR_CUDA;
   if (!mp.a_box3d) {
     g_last_error = "the CTA-pair kernel needs the 3-D activation view";
     return W4A16_ERR_CUDA;
   }
   if (!get_scratch(pr, (size_t)2 * pairs * TM * w4a16::TILE_N, p)) return W4A16_ERR_CUDA;
-  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, p), "kernel launch (CTA pairs)")) return W4A16_ERR_CUDA;
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, kern, mp.b, mp.a, mp.s, mp.c, p), "kernel launch (CTA pairs)")) return W4A16_ERR_CUDA;
   return W4A16_OK;
 }
 
@@ -559,22 +585,28 @@ const bool g_use_decode = [] {
 // the gathering epilogue is a separate instantiation, so the plain GEMM's code is untouched by it
 template <int TM, int KS>
 int launch_tc_g(const Problem &pr) {
-  if (pr.c_ld > 0)
-    return pr.groupsize == 128 ? launch_tc<TM, KS, true, true>(pr) : launch_tc<TM, KS, false, true>(pr);
-  return pr.groupsize == 128 ? launch_tc<TM, KS, true, false>(pr) : launch_tc<TM, KS, false, false>(pr);
+  using namespace w4a16;
+  const bool g = pr.groupsize == 128;
+  if (pr.c_ld > 0) return g ? launch_tc<TM, KS, true, OUT_GATHER>(pr) : launch_tc<TM, KS, false, OUT_GATHER>(pr);
+  if (use_tma_store(pr)) return g ? launch_tc<TM, KS, true, OUT_TMA>(pr) : launch_tc<TM, KS, false, OUT_TMA>(pr);
+  return g ? launch_tc<TM, KS, true, OUT_PLAIN>(pr) : launch_tc<TM, KS, false, OUT_PLAIN>(pr);
 }
 
 template <int TM, int KS>
 int launch_tc2_g(const Problem &pr) {
-  if (pr.c_ld > 0)
-    return pr.groupsize == 128 ? launch_tc2<TM, KS, true, true>(pr) : launch_tc2<TM, KS, false, true>(pr);
-  return pr.groupsize == 128 ? launch_tc2<TM, KS, true, false>(pr) : launch_tc2<TM, KS, false, false>(pr);
+  using namespace w4a16;
+  const bool g = pr.groupsize == 128;
+  if (pr.c_ld > 0) return g ? launch_tc2<TM, KS, true, OUT_GATHER>(pr) : launch_tc2<TM, KS, false, OUT_GATHER>(pr);
+  if (use_tma_store(pr)) return g ? launch_tc2<TM, KS, true, OUT_TMA>(pr) : launch_tc2<TM, KS, false, OUT_TMA>(pr);
+  return g ? launch_tc2<TM, KS, true, OUT_PLAIN>(pr) : launch_tc2<TM, KS, false, OUT_PLAIN>(pr);
 }
 
 int launch_decode_g(const Problem &pr) {
-  if (pr.c_ld > 0)
-    return pr.groupsize == 128 ? launch_single<DecodeKernel<true, true>>(pr) : launch_single<DecodeKernel<false, true>>(pr);
-  return pr.groupsize == 128 ? launch_single<DecodeKernel<true, false>>(pr) : launch_single<DecodeKernel<false, false>>(pr);
+  using namespace w4a16;
+  const bool g = pr.groupsize == 128;
+  if (pr.c_ld > 0) return g ? launch_single<DecodeKernel<true, OUT_GATHER>>(pr) : launch_single<DecodeKernel<false, OUT_GATHER>>(pr);
+  if (use_tma_store(pr)) return g ? launch_single<DecodeKernel<true, OUT_TMA>>(pr) : launch_single<DecodeKernel<false, OUT_TMA>>(pr);
+  return g ? launch_single<DecodeKernel<true, OUT_PLAIN>>(pr) : launch_single<DecodeKernel<false, OUT_PLAIN>>(pr);
 }
 
 int dispatch_tc(const Problem &pr) {

@@ -91,31 +91,12 @@ struct Params {
   int c_ld, c_col0, n_extra;
   __half *const *C_extra;
 };
-static_assert(3 * sizeof(CUtensorMap) + sizeof(Params) <= 512, "keep the kernel parameters within 512 bytes");
+static_assert(sizeof(Params) <= 128, "the kernels take four tensor maps and this block: keep it small");
 
-// Gathering epilogue: sixteen finished rows of one weight column (v: fp32 bit patterns) to C and to every further
-// destination (plain 2-byte stores, 64 contiguous bytes per warp and row; peer memory is only ever written).
-// Destinations are the outer loop, so that one pointer is live at a time.
-template <bool GROUPED>
-__device__ __forceinline__ void store_chunk_gather(const Params &p, const uint32_t (&v)[16], __half sch, int mrow0, int col) {
-  __half2 hv[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    __half lo = __float2half(__uint_as_float(v[2 * i])), hi = __float2half(__uint_as_float(v[2 * i + 1]));
-    if (!GROUPED) lo = __hmul(lo, sch), hi = __hmul(hi, sch);  // after the fp16 convert, as in the plain epilogue
-    hv[i] = __halves2half2(lo, hi);
-  }
-  const size_t off0 = (size_t)mrow0 * p.c_ld + p.c_col0 + col;
-  const int rows = p.m - mrow0;   // rows of this chunk that exist (may exceed 16)
-  for (int d = 0; d <= p.n_extra; ++d) {
-    __half *dst = (d == 0 ? p.C : p.C_extra[d - 1]) + off0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (2 * i < rows) dst[(size_t)(2 * i) * p.c_ld] = __low2half(hv[i]);
-      if (2 * i + 1 < rows) dst[(size_t)(2 * i + 1) * p.c_ld] = __high2half(hv[i]);
-    }
-  }
-}
+// How a finished tile reaches C (template parameter OUT of the kernels)
+constexpr int OUT_PLAIN = 0;    // 2-byte global stores from registers, 64 contiguous bytes per warp and row
+constexpr int OUT_GATHER = 1;   // staged in shared memory, written by rows to C and to the other ranks' buffers
+constexpr int OUT_TMA = 2;      // staged in shared memory, one cp.async.bulk.tensor store per 16-row x 128-column chunk
 
 // Gathering epilogue, cooperative form used by the epilogue warps.  A warp owns 32 weight columns (its TMEM lane
 // quadrant), so on its own it can only write 64 contiguous bytes per output row, and peer stores of that size reach
@@ -156,10 +137,43 @@ __device__ __forceinline__ bool store_chunk_gather4(const Params &p, const uint3
   return true;
 }
 
+// TMA-store epilogue (the reference stages its tile through shared memory and writes 16-byte rows,
+// marlin_cute_trait.h:754-799; here the copy engine writes the rows).  The four epilogue warps stage a 16-row chunk
+// of the 128-column tile as fp16 rows of 256 bytes -- the box of the tensor map over C, whose bounds clip the rows past
+// m -- and one thread issues the store.  Two slabs alternate as in store_chunk_gather4; the slab of chunk c is free
+// for chunk c + 2 once every warp has passed gfull[(c+1)&1], because the issuing thread arrives there only after the
+// store of chunk c has finished reading shared memory.  Returns false when the (bounded) wait ran out.
+template <bool GROUPED>
+__device__ __forceinline__ bool store_chunk_tma(const Params &p, const CUtensorMap *tmC, const uint32_t (&v)[16], __half sch,
+                                                int mrow0, int n0, int quad, int lane, __half *slabs, uint32_t gfull_bar,
+                                                int &gcount, volatile int *abort) {
+  const int buf = gcount & 1;
+  __half *sb = slabs + buf * 16 * TILE_N;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    __half h = __float2half(__uint_as_float(v[i]));
+    if (!GROUPED) h = __hmul(h, sch);  // after the fp16 convert, as in the plain epilogue
+    sb[i * TILE_N + quad * 32 + lane] = h;
+  }
+  sm100::fence_proxy_async_smem();
+  const bool issuer = (quad == 0 && lane == 0);
+  if (issuer) sm100::tma_store_wait_read();
+  __syncwarp();
+  if (lane == 0) sm100::mbar_arrive(gfull_bar + 8 * buf);
+  const bool ok = sm100::mbar_wait(gfull_bar + 8 * buf, (gcount >> 1) & 1, abort, p.wait_ns);
+  ++gcount;
+  if (!__all_sync(0xffffffffu, ok)) return false;
+  if (issuer) {
+    sm100::tma_store_2d(tmC, p.c_col0 + n0, mrow0, sm100::smem_u32(sb));
+    sm100::tma_store_commit();
+  }
+  return true;
+}
+
 // Tile configuration.  TM = batch tile (UMMA N); KS = k per pipeline stage.  The stage is the unit of
 // every hand-off; it is made large (256 k for small TM) because issuing a TMA costs the producer
 // 100+ clocks whatever its size, so bytes per TMA instruction is what bounds the load rate.
-template <int TM, int KS, bool GATHER = false>
+template <int TM, int KS, int OUT = OUT_PLAIN>
 struct Config {
   static_assert(TM == 16 || TM == 32 || TM == 64 || TM == 128 || TM == 192, "batch tile");
   static_assert(KS == 64 || KS == 128 || KS == 256, "k per stage");
@@ -181,7 +195,7 @@ struct Config {
   static constexpr int WBUFS = WBUFS_RAW > 8 ? 8 : WBUFS_RAW;  // TMEM operand ring depth
   static_assert(WBUFS >= 2, "TMEM budget");
   static constexpr int BAR_BYTES = 1024;
-  static constexpr int GATHER_BYTES = GATHER ? GATHER_SLAB_BYTES : 0;   // output staging of the gathering epilogue
+  static constexpr int GATHER_BYTES = OUT != OUT_PLAIN ? GATHER_SLAB_BYTES : 0;   // output staging of the gathering / TMA-store epilogue
   static constexpr int SMEM_MAX = 227 * 1024;
   static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - GATHER_BYTES - 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
@@ -220,6 +234,62 @@ __device__ __forceinline__ void give_up(const Params &p, volatile int *abort, in
   atomicCAS(p.status, 0, STATUS_TIMEOUT | (site << 8));
 }
 
+// Finisher of a split tile: add to v the sixteen rows at row c0 of the slices that `count` other CTAs left in the
+// scratch (slots first_slot, first_slot + slot_stride, ...: ascending, so the sum is deterministic), FLY slices in
+// flight together, re-reading until none shows the idle pattern, and put the idle pattern back so that the scratch is
+// idle again for the next launch.  `rows` = rows per slot.  Returns false when the bounded wait ran out.
+template <int FLY>
+__device__ __forceinline__ bool fold_partial_slices(uint32_t (&v)[16], uint32_t *partials, int rows, int c0, int row,
+                                                    int first_slot, int slot_stride, int count, volatile int *abort,
+                                                    uint64_t t0, uint64_t wait_ns) {
+  using namespace sm100;
+  for (int j = 0; j < count; j += FLY) {
+    uint32_t *src[FLY];
+#pragma unroll
+    for (int f = 0; f < FLY; ++f)
+      src[f] = partials + ((size_t)(first_slot + min(j + f, count - 1) * slot_stride) * rows + c0) * TILE_N + row;
+    uint32_t x[FLY][16];
+    for (uint32_t spin = 0;; ++spin) {
+#ifdef W4A16_TRACE
+      if (g_trace && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 12) {
+        g_trace[4096 + blockIdx.x * 16 + 12] = spin + 1;                                   // poll rounds
+        if (spin == 1 && j == 0) g_trace[blockIdx.x * 16 + 14] = globaltimer_ns();         // first poll came back
+      }
+#endif
+      bool up = true;
+#pragma unroll
+      for (int f = 0; f < FLY; ++f)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[f][i] = ld_slot(src[f] + (size_t)i * TILE_N);
+#pragma unroll
+      for (int f = 0; f < FLY; ++f)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
+      if (__all_sync(0xffffffffu, up)) break;
+      if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > wait_ns)) return false;
+    }
+#pragma unroll
+    for (int f = 0; f < FLY; ++f) {
+      if (j + f < count) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(x[f][i]));
+          st_slot(src[f] + (size_t)i * TILE_N, PARTIAL_IDLE);   // back to idle for the next launch
+        }
+      }
+    }
+  }
+  return true;
+}
+// The same as a real call: a kernel whose hot loops fill its register budget keeps the FLY x 16 loaded values out of
+// them this way (the call happens once per split tile).
+template <int FLY>
+__device__ __noinline__ bool fold_partial_slices_call(uint32_t (&v)[16], uint32_t *partials, int rows, int c0, int row,
+                                                      int first_slot, int slot_stride, int count, volatile int *abort,
+                                                      uint64_t t0, uint64_t wait_ns) {
+  return fold_partial_slices<FLY>(v, partials, rows, c0, row, first_slot, slot_stride, count, abort, t0, wait_ns);
+}
+
 // int4 -> fp16 exactly (zero point 8), two weights per instruction, as in the reference's dequant
 // (marlin_cute_trait.h:8-39): OR the nibble into the mantissa of 1024.0 and subtract 1032; the high
 // nibbles carry a factor 16 folded into one fma.
@@ -239,17 +309,18 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 scale, uint32_t
   hi = *reinterpret_cast<uint32_t *>(&b);
 }
 
-template <int TM, int KS, bool GROUPED, bool GATHER = false>
+template <int TM, int KS, bool GROUPED, int OUT = OUT_PLAIN>
 __global__ void __launch_bounds__(Config<TM, KS>::THREADS, 1)
 w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
-                const __grid_constant__ CUtensorMap tmS, const Params p) {
-  using Cfg = Config<TM, KS, GATHER>;
+                const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmC, const Params p) {
+  using Cfg = Config<TM, KS, OUT>;
+  constexpr bool GATHER = OUT == OUT_GATHER;
   using namespace sm100;
   constexpr int S = Cfg::STAGES;
   constexpr int NDQ = Cfg::NDQ;
   // dequant warps help to finish a split tile (see the epilogue); not in the gathering form, whose four epilogue
   // warps write every chunk together
-  constexpr bool HELP = TM >= 64 && !GATHER;
+  constexpr bool HELP = TM >= 64 && OUT == OUT_PLAIN;
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;
   constexpr uint32_t STAGE_TX = Cfg::W_BYTES + Cfg::A_BYTES + (GROUPED ? Cfg::S_BYTES : 0);
 
@@ -465,47 +536,14 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
           uint32_t v[16];
           tmem_ld_32x32b_x16(t_acc + c0, v);
           tc_wait_ld();
-          for (int c = (int)blockIdx.x + 1; c <= last_contrib && ok; c += 2) {
-            uint32_t *src[2];
-#pragma unroll
-            for (int f = 0; f < 2; ++f) src[f] = p.partials + ((size_t)min(c + f, last_contrib) * TM + c0) * TILE_N + row;
-            uint32_t x[2][16];
-            for (uint32_t spin = 0;; ++spin) {
-              bool up = true;
-#pragma unroll
-              for (int f = 0; f < 2; ++f)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) x[f][i] = ld_slot(src[f] + (size_t)i * TILE_N);
-#pragma unroll
-              for (int f = 0; f < 2; ++f)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
-              if (__all_sync(0xffffffffu, up)) break;
-              if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > p.wait_ns)) { ok = false; break; }
-            }
-            if (!ok) break;
-#pragma unroll
-            for (int f = 0; f < 2; ++f) {
-              if (c + f <= last_contrib) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(x[f][i]));
-                  st_slot(src[f] + (size_t)i * TILE_N, PARTIAL_IDLE);
-                }
-              }
-            }
-          }
+          ok = fold_partial_slices<2>(v, p.partials, TM, c0, row, (int)blockIdx.x + 1, 1, last_contrib - (int)blockIdx.x, abort, t0, p.wait_ns);
           if (!ok) break;
-          if constexpr (GATHER) {
-            store_chunk_gather<GROUPED>(p, v, sch, m0 + c0, n0 + row);
-          } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int mm = m0 + c0 + i;
-              __half h = __float2half(__uint_as_float(v[i]));
-              if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
-              if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
-            }
+          for (int i = 0; i < 16; ++i) {   // (never the gathering form: HELP is off there)
+            const int mm = m0 + c0 + i;
+            __half h = __float2half(__uint_as_float(v[i]));
+            if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
+            if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
           }
         }
         if (!ok) give_up(p, abort, 9);
@@ -556,42 +594,20 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 16; ++i) st_slot(part + (size_t)(c0 + i) * TILE_N, v[i] == PARTIAL_IDLE ? 0x7fffffffu : v[i]);
         } else {
-          // fixed summation order (ascending contributor) keeps the result deterministic; FLY contributors'
-          // slices are read together and re-read until none shows the idle pattern
-          for (int c = (int)blockIdx.x + 1; c <= last_contrib && ok; c += FLY) {
-            uint32_t *src[FLY];
-#pragma unroll
-            for (int f = 0; f < FLY; ++f)
-              src[f] = p.partials + ((size_t)min(c + f, last_contrib) * TM + c0) * TILE_N + row;
-            uint32_t x[FLY][16];
-            for (uint32_t spin = 0;; ++spin) {
-              bool up = true;
-#pragma unroll
-              for (int f = 0; f < FLY; ++f)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) x[f][i] = ld_slot(src[f] + (size_t)i * TILE_N);
-#pragma unroll
-              for (int f = 0; f < FLY; ++f)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
-              if (__all_sync(0xffffffffu, up)) break;
-              if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > p.wait_ns)) { ok = false; break; }
-            }
-            if (!ok) break;
-#pragma unroll
-            for (int f = 0; f < FLY; ++f) {
-              if (c + f <= last_contrib) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(x[f][i]));
-                  st_slot(src[f] + (size_t)i * TILE_N, PARTIAL_IDLE);   // back to idle for the next launch
-                }
-              }
-            }
-          }
+          // fixed summation order (ascending contributor) keeps the result deterministic
+          // (narrow tiles take four slices at a time through a real call: inlined, their 64 loaded values spilled
+          // registers of the main loops)
+          if (ncontrib > 0)
+            ok = TM <= 32 ? fold_partial_slices_call<FLY>(v, p.partials, TM, c0, row, (int)blockIdx.x + 1, 1, ncontrib, abort, t0, p.wait_ns)
+                          : fold_partial_slices<FLY>(v, p.partials, TM, c0, row, (int)blockIdx.x + 1, 1, ncontrib, abort, t0, p.wait_ns);
           if (!ok) break;
           if constexpr (GATHER) {
             if (!store_chunk_gather4<GROUPED>(p, v, sch, m0 + c0, n0, quad, lane, slabs, smem_u32(&bars->gfull[0]), gcount, abort)) {
+              ok = false;
+              break;
+            }
+          } else if constexpr (OUT == OUT_TMA) {
+            if (!store_chunk_tma<GROUPED>(p, &tmC, v, sch, m0 + c0, n0, quad, lane, slabs, smem_u32(&bars->gfull[0]), gcount, abort)) {
               ok = false;
               break;
             }
@@ -614,6 +630,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
       it += ke - kb;
       if (warp == NDQ) W4A16_STAMP(8);     // (last value wins) epilogue of the last segment done
     }
+    // the TMA stores of this thread have left shared memory and reached C before the CTA ends (also after a give-up)
+    if (OUT == OUT_TMA && quad == 0 && lane == 0) tma_store_wait_all();
   } else if (warp == PRODUCER_WARP) {
     // =========================================================== TMA producer (rest of the ring)
     // The whole warp runs the loop (warp-uniform operands); one elected lane issues.

@@ -19,7 +19,7 @@
 
 namespace w4a16 {
 
-template <int TM, int KS_ = 128, bool GATHER = false>
+template <int TM, int KS_ = 128, int OUT = OUT_PLAIN>
 struct Config2 {
   static_assert(TM == 32 || TM == 64 || TM == 128 || TM == 192, "batch tile of the pair");
   static_assert(KS_ == 128 || KS_ == 256, "k per stage");
@@ -39,7 +39,7 @@ struct Config2 {
   static constexpr int WBUFS = WBUFS_RAW > 4 ? 4 : WBUFS_RAW;
   static_assert(WBUFS >= 2, "TMEM budget");
   static constexpr int BAR_BYTES = 1024;
-  static constexpr int GATHER_BYTES = GATHER ? GATHER_SLAB_BYTES : 0;
+  static constexpr int GATHER_BYTES = OUT != OUT_PLAIN ? GATHER_SLAB_BYTES : 0;
   static constexpr int SMEM_MAX = 227 * 1024;
   static constexpr int STAGES_RAW = (SMEM_MAX - BAR_BYTES - GATHER_BYTES - 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
@@ -113,15 +113,16 @@ __device__ __forceinline__ int tile_width(const Params &p, int m0) {
   return max(16, (rows + 15) & ~15);
 }
 
-template <int TM, int KS_, bool GROUPED, bool GATHER = false>
+template <int TM, int KS_, bool GROUPED, int OUT = OUT_PLAIN>
 __global__ void __launch_bounds__(Config2<TM, KS_>::THREADS, 1)
 w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
-                 const __grid_constant__ CUtensorMap tmS, const Params p) {
-  using Cfg = Config2<TM, KS_, GATHER>;
+                 const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmC, const Params p) {
+  using Cfg = Config2<TM, KS_, OUT>;
+  constexpr bool GATHER = OUT == OUT_GATHER;
   using namespace sm100;
   constexpr int S = Cfg::STAGES, NDQ = Cfg::NDQ, KS = Cfg::KS;
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;
-  constexpr bool HELP = TM >= 64 && !GATHER;   // dequant warps help to finish a split tile (as in the single-CTA kernel)
+  constexpr bool HELP = TM >= 64 && OUT == OUT_PLAIN;   // dequant warps help to finish a split tile (as in the single-CTA kernel)
   constexpr uint32_t WS_TX = Cfg::W_BYTES + (GROUPED ? Cfg::S_BYTES : 0);
 
   extern __shared__ uint8_t smem_raw[];
@@ -278,48 +279,15 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
           uint32_t v[16];
           tmem_ld_32x32b_x16(t_acc + c0, v);
           tc_wait_ld();
-          for (int cp = pair + 1; cp <= last_pair && ok; cp += 2) {
-            uint32_t *src[2];
-#pragma unroll
-            for (int f = 0; f < 2; ++f)
-              src[f] = p.partials + ((size_t)(2 * min(cp + f, last_pair) + (int)rank) * TM + c0) * TILE_N + row;
-            uint32_t x[2][16];
-            for (uint32_t spin = 0;; ++spin) {
-              bool up = true;
-#pragma unroll
-              for (int f = 0; f < 2; ++f)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) x[f][i] = ld_slot(src[f] + (size_t)i * TILE_N);
-#pragma unroll
-              for (int f = 0; f < 2; ++f)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
-              if (__all_sync(0xffffffffu, up)) break;
-              if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > p.wait_ns)) { ok = false; break; }
-            }
-            if (!ok) break;
-#pragma unroll
-            for (int f = 0; f < 2; ++f) {
-              if (cp + f <= last_pair) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(x[f][i]));
-                  st_slot(src[f] + (size_t)i * TILE_N, PARTIAL_IDLE);
-                }
-              }
-            }
-          }
+          // contributors are the same-rank CTAs of the following pairs: slots 2 (pair + 1) + rank, + 2, ...
+          ok = fold_partial_slices<2>(v, p.partials, TM, c0, row, 2 * (pair + 1) + (int)rank, 2, last_pair - pair, abort, t0, p.wait_ns);
           if (!ok) break;
-          if constexpr (GATHER) {
-            store_chunk_gather<GROUPED>(p, v, sch, m0 + c0, n0 + row);
-          } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int mm = m0 + c0 + i;
-              __half h = __float2half(__uint_as_float(v[i]));
-              if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
-              if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
-            }
+          for (int i = 0; i < 16; ++i) {   // (never the gathering form: HELP is off there)
+            const int mm = m0 + c0 + i;
+            __half h = __float2half(__uint_as_float(v[i]));
+            if (!GROUPED) h = __hmul(h, sch);  // per-channel scale after the fp16 convert (marlin_cute_trait.h:764-769)
+            if (mm < p.m) p.C[(size_t)mm * p.n + n0 + row] = h;
           }
         }
         if (!ok) give_up(p, abort, 19);
@@ -366,40 +334,15 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 16; ++i) st_slot(part + (size_t)(c0 + i) * TILE_N, v[i] == PARTIAL_IDLE ? 0x7fffffffu : v[i]);
         } else {
-          for (int cp = pair + 1; cp <= last_pair && ok; cp += FLY) {
-            uint32_t *src[FLY];
-#pragma unroll
-            for (int f = 0; f < FLY; ++f)
-              src[f] = p.partials + ((size_t)(2 * min(cp + f, last_pair) + (int)rank) * TM + c0) * TILE_N + row;
-            uint32_t x[FLY][16];
-            for (uint32_t spin = 0;; ++spin) {
-              bool up = true;
-#pragma unroll
-              for (int f = 0; f < FLY; ++f)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) x[f][i] = ld_slot(src[f] + (size_t)i * TILE_N);
-#pragma unroll
-              for (int f = 0; f < FLY; ++f)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
-              if (__all_sync(0xffffffffu, up)) break;
-              if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > p.wait_ns)) { ok = false; break; }
-            }
-            if (!ok) break;
-#pragma unroll
-            for (int f = 0; f < FLY; ++f) {
-              if (cp + f <= last_pair) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(x[f][i]));
-                  st_slot(src[f] + (size_t)i * TILE_N, PARTIAL_IDLE);
-                }
-              }
-            }
-          }
+          if (ncontrib > 0) ok = fold_partial_slices<FLY>(v, p.partials, TM, c0, row, 2 * (pair + 1) + (int)rank, 2, ncontrib, abort, t0, p.wait_ns);
           if (!ok) break;
           if constexpr (GATHER) {
             if (!store_chunk_gather4<GROUPED>(p, v, sch, m0 + c0, n0, quad, lane, slabs, smem_u32(&bars->gfull[0]), gcount, abort)) {
+              ok = false;
+              break;
+            }
+          } else if constexpr (OUT == OUT_TMA) {
+            if (!store_chunk_tma<GROUPED>(p, &tmC, v, sch, m0 + c0, n0, quad, lane, slabs, smem_u32(&bars->gfull[0]), gcount, abort)) {
               ok = false;
               break;
             }
@@ -419,6 +362,8 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->accempty[acc]), 0));
     }
+    // the TMA stores of this thread have left shared memory and reached C before the CTA ends (also after a give-up)
+    if (OUT == OUT_TMA && quad == 0 && lane == 0) tma_store_wait_all();
   } else if (warp == PRODUCER_WARP) {
     // =========================================================== TMA producer (one per CTA, each for its own halves)
     const int first = min(S, nsteps);

@@ -34,10 +34,10 @@
 
 namespace w4a16 {
 
-template <bool GATHER = false, int CL = 1>
+template <int OUT = OUT_PLAIN, int CL = 1>
 struct DecodeConfig {
   static_assert(CL == 1 || CL == 2 || CL == 4 || CL == 8, "cluster size along k");
-  static_assert(CL == 1 || !GATHER, "the gathering epilogue runs on the stream-K form");
+  static_assert(CL == 1 || OUT != OUT_GATHER, "the gathering epilogue runs on the stream-K form");
   static constexpr int TM = 16;                              // batch tile = UMMA N
   static constexpr int KS = 256;                             // k per stage
   static constexpr int KCHUNKS = KS / 64;
@@ -59,7 +59,8 @@ struct DecodeConfig {
   static_assert(NACC == NMMA && WBUFS == NMMA, "issuer i owns operand buffer i and accumulator set i");
   static constexpr int THREADS = (NDQ + EPI_WARPS + 1 + NMMA) * 32;
   static constexpr int BAR_BYTES = 1024;
-  static constexpr int GATHER_BYTES = GATHER ? GATHER_SLAB_BYTES : 0;
+  // output staging: two padded slabs for the gathering epilogue, one 4 KB slab for the TMA store (a tile is one chunk)
+  static constexpr int GATHER_BYTES = OUT == OUT_GATHER ? GATHER_SLAB_BYTES : OUT == OUT_TMA ? 2 * 16 * TILE_N * 2 : 0;
   // cluster form: the other ranks' fp32 partial tiles land here, in rank 0's shared memory: [CL - 1][TM][128] fp32
   static constexpr int XSLAB_BYTES = (CL - 1) * TM * TILE_N * 4;
   static constexpr int SMEM_MAX = 227 * 1024;
@@ -85,61 +86,17 @@ struct DecodeBars {  // lives in shared memory
 };
 static_assert(sizeof(DecodeBars) <= 1024, "barrier block");
 
-// Finisher of a split tile: add the sixteen rows at row c0 of the slices that CTAs [first, last] left in the scratch
-// to v (ascending CTA order: deterministic), FLY slices in flight together, re-reading until none shows the idle
-// pattern, and put the idle pattern back.  `rows` = rows per slot.  Returns false when the bounded wait ran out.
-template <int FLY>
-__device__ __noinline__ bool fold_partial_slices(uint32_t (&v)[16], uint32_t *partials, int rows, int c0, int row,
-                                                    int first, int last, volatile int *abort, uint64_t t0, uint64_t wait_ns) {
-  using namespace sm100;
-  for (int c = first; c <= last; c += FLY) {
-    uint32_t *src[FLY];
-#pragma unroll
-    for (int f = 0; f < FLY; ++f) src[f] = partials + ((size_t)min(c + f, last) * rows + c0) * TILE_N + row;
-    uint32_t x[FLY][16];
-    for (uint32_t spin = 0;; ++spin) {
-#ifdef W4A16_TRACE
-      if (g_trace && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 12) {
-        g_trace[4096 + blockIdx.x * 16 + 12] = spin + 1;                                   // poll rounds
-        if (spin == 1 && c == first) g_trace[blockIdx.x * 16 + 14] = globaltimer_ns();     // first poll came back
-      }
-#endif
-      bool up = true;
-#pragma unroll
-      for (int f = 0; f < FLY; ++f)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[f][i] = ld_slot(src[f] + (size_t)i * TILE_N);
-#pragma unroll
-      for (int f = 0; f < FLY; ++f)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) up &= (x[f][i] != PARTIAL_IDLE);
-      if (__all_sync(0xffffffffu, up)) break;
-      if ((spin & 0xf) == 0xf && __any_sync(0xffffffffu, *abort || globaltimer_ns() - t0 > wait_ns)) return false;
-    }
-#pragma unroll
-    for (int f = 0; f < FLY; ++f) {
-      if (c + f <= last) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(x[f][i]));
-          st_slot(src[f] + (size_t)i * TILE_N, PARTIAL_IDLE);   // back to idle for the next launch
-        }
-      }
-    }
-  }
-  return true;
-}
-
 // CL > 1: the cluster form for layers with few tiles.  A cluster of CL CTAs (launched with that cluster dimension) owns
 // one tile and cuts its k-range CL ways; ranks 1.. send their fp32 partial tile straight into rank 0's shared memory
 // (st.shared::cluster; the data is its own flag, as in the stream-K fix-up), and rank 0 adds them in rank order and writes C.  The stream-K
 // form's fix-up goes through L2 instead, and when all CTAs of a tile finish together (which they do when a tile is cut
 // evenly) that costs the finisher two L2 round trips after everybody else is done; inside a cluster it is one hop.
-template <bool GROUPED, bool GATHER = false, int CL = 1>
+template <bool GROUPED, int OUT = OUT_PLAIN, int CL = 1>
 __global__ void __launch_bounds__(DecodeConfig<>::THREADS, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
-                    const __grid_constant__ CUtensorMap tmS, const Params p) {
-  using Cfg = DecodeConfig<GATHER, CL>;
+                    const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmC, const Params p) {
+  using Cfg = DecodeConfig<OUT, CL>;
+  constexpr bool GATHER = OUT == OUT_GATHER;
   using namespace sm100;
   constexpr int S = Cfg::STAGES, NDQ = Cfg::NDQ, TM = Cfg::TM, KS = Cfg::KS;
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;   // first of NMMA issuer warps
@@ -266,7 +223,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     if (crank == 0 && warp >= NDQ && warp < NDQ + EPI_WARPS) {
       // rank 0's epilogue warps, idle for the next microseconds, put the idle pattern into the slab; their arrive
       // releases it at cluster scope (that release is what costs ~1500 clocks: nobody else pays it)
-      uint32_t *cell = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES) + (warp - NDQ) * 32 + lane;
+      uint32_t *cell = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES + Cfg::GATHER_BYTES) + (warp - NDQ) * 32 + lane;
 #pragma unroll 4
       for (int i = 0; i < (CL - 1) * TM; ++i) cell[(size_t)i * TILE_N] = PARTIAL_IDLE;
       cluster_arrive();
@@ -360,7 +317,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     const uint32_t sS_u = smem_u32(sS);
     pdl_wait_prior_grid();   // C and the partial-tile scratch may still be in use by the previous kernel
     __half *slabs = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES);   // gathering form only
-    float *xslab = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES);     // cluster form only
+    float *xslab = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + Cfg::BAR_BYTES + Cfg::GATHER_BYTES);   // cluster form only
     int gcount = 0;
     int step = 0;
     bool ok = true;
@@ -458,7 +415,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
           if (warp == NDQ) W4A16_STAMP(7);             // partial tiles folded in
         } else if (ncontrib > 0) {
           const uint64_t t0 = globaltimer_ns();
-          if (!fold_partial_slices<3>(v, p.partials, TM, 0, row, (int)blockIdx.x + 1, last_contrib, abort, t0, p.wait_ns)) {
+          if (!fold_partial_slices_call<3>(v, p.partials, TM, 0, row, (int)blockIdx.x + 1, 1, ncontrib, abort, t0, p.wait_ns)) {
             give_up(p, abort, 4);
             ok = false;
             break;
@@ -467,6 +424,12 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
         }
         if constexpr (GATHER) {
           if (!store_chunk_gather4<GROUPED>(p, v, sch, m0, n0, quad, lane, slabs, smem_u32(&bars->gfull[0]), gcount, abort)) {
+            give_up(p, abort, 4);
+            ok = false;
+            break;
+          }
+        } else if constexpr (OUT == OUT_TMA) {
+          if (!store_chunk_tma<GROUPED>(p, &tmC, v, sch, m0, n0, quad, lane, slabs, smem_u32(&bars->gfull[0]), gcount, abort)) {
             give_up(p, abort, 4);
             ok = false;
             break;
@@ -484,6 +447,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       it += ke - kb;
       if (warp == NDQ) W4A16_STAMP(8);     // (last value wins) epilogue of the last segment done
     }
+    // the TMA stores of this thread have left shared memory and reached C before the CTA ends (also after a give-up)
+    if (OUT == OUT_TMA && quad == 0 && lane == 0) tma_store_wait_all();
   } else if (warp == PRODUCER_WARP) {
     // =========================================================== TMA producer (rest of the ring)
     long long c_wait = 0, c_issue = 0;

@@ -52,9 +52,9 @@ COPIES = 3
 METRIC = "w4a16_weight_hbm_gbs_m16"
 UNIT = "GB/s"
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from one ncu capture of each of the step's
-# four kernels: 26.16, 9.21, 46.68 and 23.76 MB, mean 26.45 MB.  It is a property of the access pattern (every
+# four kernels: 26.15, 8.82, 46.68 and 23.64 MB, mean 26.32 MB.  It is a property of the access pattern (every
 # weight byte is read once), re-captured whenever the decode kernel's loads change.
-NCU_DRAM_BYTES_PER_LAUNCH = 26.45e6
+NCU_DRAM_BYTES_PER_LAUNCH = 26.32e6
 WORKLOAD = "llama2-7b linears (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)}, M=16, g128"
 # the same for both arms, so that their lines describe one configuration
 CONFIG = {
@@ -286,7 +286,11 @@ class Ctx:
         return ms[len(ms) // 2], ms[0], replays
 
     def time_graph(self, fn, reps, **kw):
+        """An extra's figure: graph of `reps` calls, median replay, max over ranks.  The legs follow one another
+        after a short pause, so that a leg that ran the part at its power cap (prefill) does not set the clocks
+        and temperatures the next one (HBM-bound) starts from."""
         g = self.capture(fn, reps)
+        time.sleep(0.25)
         med, best, _ = self.time_replays(g, reps, **kw)
         return self.max_over_ranks(med)
 
