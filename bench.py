@@ -552,9 +552,12 @@ def measure_gathered_step(ctx, args, step, layers, acts, outs, wss):
         pkg.device_status(ctx.local)
         step(args.steps - 1)
         torch.cuda.synchronize()
-        same = all(torch.equal(pbufs[li].local[:, rank * n:(rank + 1) * n], outs[li]) for li, (n, _) in enumerate(SHAPES))
+        # (not bit for bit: the plain GEMM may run the cluster form, whose partial tiles are added in another order)
+        diff = max(float((pbufs[li].local[:, rank * n:(rank + 1) * n].float() - outs[li].float()).abs().max())
+                   for li, (n, _) in enumerate(SHAPES))
+        scale = max(float(o.float().abs().max()) for o in outs)
         gathered["fused"] = {"value": world * wbytes / (fms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": fms,
-                             "own_columns_match_plain_gemm": bool(same),
+                             "own_columns_vs_plain_gemm_max_abs_diff": ctx.max_over_ranks(diff), "bound": 1e-2 * scale,
                              "note": "graph replays; epilogue stores to all ranks' buffers + barrier kernel per layer, no NCCL"}
     except Exception as exc:
         gathered["fused"] = {"unavailable": str(exc)[:200]}
@@ -612,11 +615,14 @@ def measure_sharded70b(ctx):
                         fms = ctx.time_graph(fused, reps, min_ms=20.0)
                         pkg.device_status(ctx.local)
                         # the last captured call used copy (reps - 1) % copies: the plain GEMM on it must give this
-                        # rank's columns of the gathered buffer bit for bit
+                        # rank's columns of the gathered buffer (to rounding: the plain GEMM may add partial tiles
+                        # in another order)
                         pkg.mul(A, Bs[(reps - 1) % copies], C, ss[(reps - 1) % copies], ws)
                         torch.cuda.synchronize()
                         res["fused_gather_us"] = round(fms * 1e3, 2)
-                        res["fused_own_columns_match"] = bool(torch.equal(pb.local[:, rank * n:(rank + 1) * n], C))
+                        own = pb.local[:, rank * n:(rank + 1) * n].float()
+                        res["fused_own_columns_max_abs_diff"] = round(ctx.max_over_ranks(float((own - C.float()).abs().max())), 5)
+                        res["fused_diff_bound"] = round(1e-2 * float(C.float().abs().max()), 4)
                         # bytes this rank's epilogue sends to the other ranks, against the link rate
                         res["fused_egress_gbs"] = round((world - 1) * 2.0 * m * n / (fms * 1e-3) / 1e9, 1)
                     except Exception as exc:
