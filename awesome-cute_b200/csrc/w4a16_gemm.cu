@@ -308,6 +308,11 @@ int launch_single(const Problem &pr) {
   int grid = pr.sms > 0 ? pr.sms : nsm;
   if (grid > nsm) grid = nsm;  // the finisher of a split tile needs its contributors co-resident
   if (grid > MAX_GRID) grid = MAX_GRID;
+  // Skinny batches whose tiles number between ~0.58 and 1 x the SMs: one whole tile per CTA and no fix-up at all beats
+  // cutting the tiles to occupy the remaining SMs (12288 x 4096 at m = 16: 9.6 us on 96 CTAs, 10.3 us on 140; the
+  // launch is latency- and HBM-bound, not SM-bound).
+  const int tiles = p.n_tiles * p.m_tiles;
+  if (pr.sms <= 0 && K::TM <= 16 && !pr.orphan_finisher && tiles <= grid && 100 * tiles >= 58 * grid) grid = tiles;
   if (grid > p.total_iters) grid = p.total_iters;
   p.iters_per_cta = (p.total_iters + grid - 1) / grid;
   grid = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
@@ -624,7 +629,10 @@ int dispatch_tc(const Problem &pr) {
     return launch_decode_g(pr);
   }
   if (pr.m <= 16) return k256 ? launch_tc_g<16, 256>(pr) : k128 ? launch_tc_g<16, 128>(pr) : launch_tc_g<16, 64>(pr);
-  // 17..32 rows on CTA pairs as well (+12-16 %)
+  // 17..32 rows on CTA pairs as well (+12-16 % over the general kernel).  The decode kernel widened to 32- and 64-row
+  // tiles (two dequant sets: the accumulator sets need the third operand buffer's tensor-memory columns) was measured
+  // 5 % slower than the pairs at 32 rows and 50-90 % slower at 64 (4096 x 4096: 9.6 / 17.9 us against 9.1 / 10.0 us):
+  // at N = 64 its sixteen MMAs per stage take 1024 tensor clocks on ONE SM, the pair spreads them over two.
   if (g_use_pairs && pr.m > 16 && pr.m <= 32 && k256 && pr.n % 256 == 0 && !pr.fixed_partials && !pr.orphan_finisher) {
     const int rc = launch_tc2_g<32, 256>(pr);
     if (rc != -2) return rc;

@@ -101,6 +101,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
   constexpr int S = Cfg::STAGES, NDQ = Cfg::NDQ, TM = Cfg::TM, KS = Cfg::KS;
   constexpr int PRODUCER_WARP = NDQ + EPI_WARPS, MMA_WARP = NDQ + EPI_WARPS + 1;   // first of NMMA issuer warps
   constexpr uint32_t STAGE_TX = Cfg::W_BYTES + Cfg::A_BYTES + (GROUPED ? Cfg::S_BYTES : 0);
+  constexpr int PRE = 3;           // stages requested before the CTA-wide sync of the prologue (one per dequant set)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -180,8 +181,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     pro_nidx = pro_tile % p.n_tiles;
     pro_m0 = (pro_tile / p.n_tiles) * TM;
     bar_arrive(1, 64);             // barriers exist: the MMA warp may issue the activation loads (it waits, we do not)
-    const int first = min(S, nsteps);
-    for (; pro_step < first; ++pro_step) {
+    // Only the first PRE stages before the CTA-wide sync: issuing a TMA costs ~100 clocks, a whole ring-full would
+    // hold the dequant warps at the sync for a microsecond, past the time the first stage lands.
+    const int pre = min(PRE, nsteps);
+    for (; pro_step < pre; ++pro_step) {
       if (elect_one()) issue_weights(pro_step, pro_nidx, pro_kk);
       __syncwarp();
       if (++pro_kk == p.k_iters) {
@@ -189,9 +192,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
         if (++pro_nidx == p.n_tiles) { pro_nidx = 0; pro_m0 += TM; }
       }
     }
-    pdl_launch_dependents();       // the next kernel may start its own prologue as SMs free up
-    pdl_wait_prior_grid();         // (the steady-state loop below issues activation loads too)
-    W4A16_STAMP(9);                // first ring-full issued
   }
   if (warp == MMA_WARP) {          // the first MMA warp owns TMEM
     if (lane == 0) { tma_prefetch_desc(&tmA); }
@@ -201,8 +201,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     pdl_wait_prior_grid();
     int tile = it_begin / p.k_iters, kk = it_begin - tile * p.k_iters;
     int m0 = (tile / p.n_tiles) * TM, nidx = tile % p.n_tiles;
-    const int first = min(S, nsteps);
-    for (int i = 0; i < first; ++i) {
+    const int pre = min(PRE, nsteps);
+    for (int i = 0; i < pre; ++i) {   // the activations of the stages whose weights the producer has requested
       if (elect_one()) issue_acts(i, m0, kk);
       __syncwarp();
       if (++kk == p.k_iters) {
@@ -452,6 +452,32 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
   } else if (warp == PRODUCER_WARP) {
     // =========================================================== TMA producer (rest of the ring)
     long long c_wait = 0, c_issue = 0;
+    {
+      // the rest of the first ring-full: weights and scales at once (parameters, never a kernel's output: legal before
+      // griddepcontrol.wait), their activations once the previous kernel of the stream has completed
+      const int first = min(S, nsteps), from = pro_step;
+      const int kk0 = pro_kk, nidx0 = pro_nidx, m00 = pro_m0;
+      for (; pro_step < first; ++pro_step) {
+        if (elect_one()) issue_weights(pro_step, pro_nidx, pro_kk);
+        __syncwarp();
+        if (++pro_kk == p.k_iters) {
+          pro_kk = 0;
+          if (++pro_nidx == p.n_tiles) { pro_nidx = 0; pro_m0 += TM; }
+        }
+      }
+      pdl_launch_dependents();       // the next kernel may start its own prologue as SMs free up
+      pdl_wait_prior_grid();
+      int kk = kk0, nidx = nidx0, m0 = m00;
+      for (int i = from; i < first; ++i) {
+        if (elect_one()) issue_acts(i, m0, kk);
+        __syncwarp();
+        if (++kk == p.k_iters) {
+          kk = 0;
+          if (++nidx == p.n_tiles) { nidx = 0; m0 += TM; }
+        }
+      }
+      W4A16_STAMP(9);                // first ring-full issued
+    }
     for (; pro_step < nsteps; ++pro_step) {
       const int st = pro_step % S;
       const long long c0 = W4A16_CLK();
