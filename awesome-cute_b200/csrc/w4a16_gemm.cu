@@ -783,9 +783,52 @@ extern "C" int w4a16_marlin_gemm(const void *A, const void *B, void *C, const vo
 }
 
 // The GEMM with HOST activations and HOST output: copy in, multiply, copy out, all enqueued on `stream`.
+//
+// Small host<->device copies through the copy engines cost about ten microseconds each on the stream (set-up and
+// completion, not bytes), which is more than a decode GEMM.  When both host buffers are page-locked (and therefore
+// addressable from the device) and the batch is small, the copies are done by the SMs instead:
+//   * a few CTAs read A_host over PCIe into A_stage; the kernel signals griddepcontrol.launch_dependents at once, so
+//     the GEMM behind it starts its prologue and weight prefetch meanwhile and waits for the copy (griddepcontrol.wait)
+//     only before it loads activations;
+//   * the GEMM's epilogue writes C rows straight into C_host (posted PCIe writes): no second copy, no C_stage.
+// That serves a caller who runs one layer after the other on ONE stream (measured: the four 7B layers at m = 16 in
+// 121 us instead of 162 us); with several streams the copy engines overlap one layer's copies with another layer's
+// kernel and the direct writes only lengthen the kernels (66 us against 59.5 us; copying only A with the SMs: 65 us), so it is opt-in:
+// W4A16_HOST_DIRECT=1 in the environment.
+namespace {
+const bool g_host_direct = [] {
+  const char *e = std::getenv("W4A16_HOST_DIRECT");
+  return e && e[0] == '1';
+}();
+
+__global__ void __launch_bounds__(512) copy_in_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, size_t n16) {
+  sm100::pdl_launch_dependents();   // the GEMM behind this kernel orders itself with griddepcontrol.wait
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) dst[i] = src[i];
+}
+
+// device address of a page-locked host buffer, or null when the buffer is pageable (looked up once per pointer)
+void *device_view_of_host(const void *host) {
+  static std::map<const void *, void *> cache;   // guarded by g_mu
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = cache.find(host);
+  if (it != cache.end()) return it->second;
+  void *dptr = nullptr;
+  cudaPointerAttributes attr{};
+  if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+    dptr = attr.devicePointer;
+  else
+    cudaGetLastError();   // a pageable pointer is not an error here
+  if (cache.size() >= 4096) cache.clear();
+  cache[host] = dptr;
+  return dptr;
+}
+}  // namespace
+
 extern "C" int w4a16_marlin_gemm_host(const void *A_host, const void *B, void *C_host, const void *s, int prob_m,
                                       int prob_n, int prob_k, void *workspace, int groupsize, int dev, void *stream,
                                       void *A_stage, void *C_stage) {
+  const int sms = -1;
   if (prob_m < 0 || prob_n < 0 || prob_k < 0) return W4A16_ERR_ARG;
   int tk = -1, tn = -1;
   const int chk = check_problem(prob_m, prob_n, prob_k, groupsize, tk, tn);
@@ -793,11 +836,20 @@ extern "C" int w4a16_marlin_gemm_host(const void *A_host, const void *B, void *C
   if (chk != W4A16_OK) return chk;
   if (!A_host || !C_host || !A_stage || !C_stage) return W4A16_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (!cuda_ok(cudaMemcpyAsync(A_stage, A_host, sizeof(__half) * (size_t)prob_m * prob_k, cudaMemcpyHostToDevice, st),
-               "cudaMemcpyAsync(A)"))
+  const size_t a_bytes = sizeof(__half) * (size_t)prob_m * prob_k;
+  if (g_host_direct && prob_m <= 64 && (a_bytes & 15) == 0 && !(reinterpret_cast<uintptr_t>(A_stage) & 15)) {
+    void *dA = device_view_of_host(A_host), *dC = device_view_of_host(C_host);
+    if (dA && dC && !((reinterpret_cast<uintptr_t>(dA) | reinterpret_cast<uintptr_t>(dC)) & 15)) {
+      if (!device_is_current(dev)) return W4A16_ERR_ARG;
+      copy_in_kernel<<<4, 512, 0, st>>>(static_cast<const uint4 *>(dA), static_cast<uint4 *>(A_stage), a_bytes / 16);
+      if (!cuda_ok(cudaGetLastError(), "copy-in launch")) return W4A16_ERR_CUDA;
+      return gemm_entry(false, A_stage, B, dC, s, prob_m, prob_n, prob_k, workspace, groupsize, dev, st, -1, -1, sms, 16);
+    }
+  }
+  if (!cuda_ok(cudaMemcpyAsync(A_stage, A_host, a_bytes, cudaMemcpyHostToDevice, st), "cudaMemcpyAsync(A)"))
     return W4A16_ERR_CUDA;
   const int rc = gemm_entry(false, A_stage, B, C_stage, s, prob_m, prob_n, prob_k, workspace, groupsize, dev, st, -1, -1,
-                            -1, 16);
+                            sms, 16);
   if (rc != W4A16_OK) return rc;
   if (!cuda_ok(cudaMemcpyAsync(C_host, C_stage, sizeof(__half) * (size_t)prob_m * prob_n, cudaMemcpyDeviceToHost, st),
                "cudaMemcpyAsync(C)"))
@@ -1018,11 +1070,12 @@ extern "C" int w4a16_marlin_gemm_gather(const void *A, const void *B, const void
   pr.c_ld = n_local * world;
   pr.c_col0 = n_local * rank;
   if (world > 1) {
-    // the other ranks' buffers, as a table in device memory that is made once per distinct set of destinations
+    // the other ranks' buffers, as a table in device memory that is made once per distinct set of destinations.
+    // Order: rank + 1, rank + 2, ... (mod world), so that at any moment the ranks' stores head for different GPUs
+    // instead of all ranks writing to GPU 0 first, then to GPU 1, ...
     std::array<uintptr_t, 9> key{};
     key[0] = (uintptr_t)dev;
-    for (int r = 0; r < world; ++r)
-      if (r != rank) key[1 + pr.n_extra++] = reinterpret_cast<uintptr_t>(dst[r]);
+    for (int j = 1; j < world; ++j) key[1 + pr.n_extra++] = reinterpret_cast<uintptr_t>(dst[(rank + j) % world]);
     std::lock_guard<std::mutex> lock(g_mu);
     void *&tab = g_dst_tables[key];
     if (!tab) {

@@ -101,7 +101,7 @@ constexpr int OUT_TMA = 2;      // staged in shared memory, one cp.async.bulk.te
 // Gathering epilogue, cooperative form used by the epilogue warps.  A warp owns 32 weight columns (its TMEM lane
 // quadrant), so on its own it can only write 64 contiguous bytes per output row, and peer stores of that size reach
 // less than half of the NVLink rate.  The four epilogue warps therefore stage each 16-row chunk of the 128-column tile
-// in shared memory and write it out by rows: 256 contiguous bytes per row, 8 bytes per lane, every destination.
+// in shared memory and write it out by rows: 256 contiguous bytes per row, 16 bytes per lane, every destination.
 // Two slabs alternate; a warp may refill slab b for chunk c+2 once it has passed gfull[(c+1)&1], because every warp
 // reads chunk c before it arrives for chunk c+1.  Returns false when the (bounded) wait ran out.
 constexpr int GATHER_LD = TILE_N + 8;                       // slab row pitch in fp16 (272 bytes)
@@ -123,15 +123,17 @@ __device__ __forceinline__ bool store_chunk_gather4(const Params &p, const uint3
   const bool ok = sm100::mbar_wait(gfull_bar + 8 * buf, (gcount >> 1) & 1, abort, p.wait_ns);
   ++gcount;
   if (!__all_sync(0xffffffffu, ok)) return false;
-  const size_t col = (size_t)p.c_col0 + n0 + lane * 4;
+  // 16 bytes per lane: a half-warp writes one 256-byte row, a warp instruction two rows; this warp's rows are
+  // quad, quad + 4, quad + 8, quad + 12
+  const size_t col = (size_t)p.c_col0 + n0 + (lane & 15) * 8;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int r = quad + 4 * j, mm = mrow0 + r;
-    const uint2 val = *reinterpret_cast<const uint2 *>(sb + r * GATHER_LD + lane * 4);
+  for (int j = 0; j < 2; ++j) {
+    const int r = quad + 4 * (2 * j + (lane >> 4)), mm = mrow0 + r;
+    const uint4 val = *reinterpret_cast<const uint4 *>(sb + r * GATHER_LD + (lane & 15) * 8);
     if (mm < p.m) {
       const size_t off = (size_t)mm * p.c_ld + col;
-      *reinterpret_cast<uint2 *>(p.C + off) = val;
-      for (int d = 0; d < p.n_extra; ++d) *reinterpret_cast<uint2 *>(p.C_extra[d] + off) = val;
+      *reinterpret_cast<uint4 *>(p.C + off) = val;
+      for (int d = 0; d < p.n_extra; ++d) *reinterpret_cast<uint4 *>(p.C_extra[d] + off) = val;
     }
   }
   return true;

@@ -91,6 +91,39 @@ def mul_host(A_host, B, C_host, s, workspace, A_stage, C_stage, stream=None):
         _check(err, prob_m, prob_n, prob_k, -1, -1, groupsize)
 
 
+class HostGemm:
+    """`mul_host` with its arguments checked and converted once: a layer that is called every decode step with the
+    same pinned host buffers pays the library call only (the checks and conversions of `mul_host` cost about as much
+    as the call itself).  `op = HostGemm(A_host, B, C_host, s, workspace, A_stage, C_stage, stream)`, then `op()` per
+    step: enqueues the copy of A_host to the device, the GEMM and the copy of the result into C_host on `stream`.
+    The tensors must stay alive and in place while the object is used."""
+
+    def __init__(self, A_host, B, C_host, s, workspace, A_stage, C_stage, stream=None):
+        prob_m, prob_k = A_host.shape
+        prob_n = C_host.shape[1]
+        groupsize = -1 if s.shape[0] == 1 else prob_k // s.shape[0]
+        if groupsize != -1 and groupsize * s.shape[0] != prob_k:
+            raise RuntimeError("k=%d not compatible with %d groups." % (prob_k, s.shape[0]))
+        if workspace.numel() < prob_n // 128 * 16:
+            raise RuntimeError("workspace must be of size at least %d." % (prob_n // 128 * 16))
+        if A_host.is_cuda or C_host.is_cuda or not B.is_cuda:
+            raise RuntimeError("HostGemm takes host activations/outputs and device weights.")
+        dev = B.get_device()
+        st = stream if stream is not None else torch.cuda.current_stream(dev)
+        self._keep = (A_host, B, C_host, s, workspace, A_stage, C_stage, st)
+        self._shape = (prob_m, prob_n, prob_k, groupsize)
+        self._dev = dev
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        self._args = (vp(A_host.data_ptr()), vp(B.data_ptr()), vp(C_host.data_ptr()), vp(s.data_ptr()), ci(prob_m), ci(prob_n),
+                      ci(prob_k), vp(workspace.data_ptr()), ci(groupsize), ci(dev), vp(st.cuda_stream), vp(A_stage.data_ptr()),
+                      vp(C_stage.data_ptr()))
+
+    def __call__(self):
+        err = _L.w4a16_marlin_gemm_host(*self._args)     # the library checks that the device is current
+        if err:
+            _check(err, self._shape[0], self._shape[1], self._shape[2], -1, -1, self._shape[3])
+
+
 def mul_gather(A, B, s, workspace, dst_ptrs, rank):
     """Column-shard GEMM whose epilogue writes this rank's columns into every rank's [m, world * n_local] buffer
     (w4a16_marlin_gemm_gather).  dst_ptrs: device addresses of the `world` destination buffers as seen from this

@@ -100,10 +100,16 @@ int w4a16_marlin_gemm_builtin_scratch(const void *A, const void *B, void *C, con
  * resident, as the reference's Layer keeps them, gemm/marlin_gemm/marlin.py:82-85).  It is the host-tensor
  * form of the reference's  mul()  (gemm/marlin_gemm/marlin.py:11-24), which the reference only offers for
  * device tensors.  Returns like w4a16_marlin_gemm; the caller synchronises `stream` before reading C_host.
+ * With W4A16_HOST_DIRECT=1 in the environment, page-locked host buffers and prob_m <= 64, the copies do not go through
+ * the copy engines (about ten microseconds of stream time each, more than a decode GEMM): a small kernel reads A_host
+ * over PCIe into A_stage while the GEMM behind it already prefetches its weights, and the GEMM writes its result rows
+ * straight into C_host; C_stage is then not touched.  It pays on a single stream (layers run one after the other) and
+ * costs where several streams already overlap copies with kernels, hence opt-in.
  */
 int w4a16_marlin_gemm_host(const void *A_host, const void *B, void *C_host, const void *s, int prob_m, int prob_n,
                            int prob_k, void *workspace, int groupsize, int dev, void *stream, void *A_stage,
                            void *C_stage);
+
 
 /* ---- column-sharded GEMM with a gathering epilogue (one process per GPU).  The reference is single-GPU and has
  * no counterpart; the shard rule follows from its layout (gemm/marlin_gemm/marlin.py:29-57: both permutations stay

@@ -207,7 +207,17 @@ def test_mul_host_copies_in_and_out():
     for _ in range(2):
         pkg.mul_host(hA, Bt, hC, st, ws, A_stage, C_stage)
     pkg.device_status(0)
-    check(hC, orc.c_gemm(A, q, s, gs), "mul_host")
+    want = orc.c_gemm(A, q, s, gs)
+    check(hC, want, "mul_host")
+    # the same call with its arguments prepared once, on a stream of its own
+    side = torch.cuda.Stream(device=DEV)
+    hC2 = torch.zeros((m, n), dtype=torch.half).pin_memory()
+    op = pkg.HostGemm(hA, Bt, hC2, st, ws, A_stage, C_stage, stream=side)
+    for _ in range(3):
+        op()
+    side.synchronize()
+    check(hC2, want, "HostGemm")
+    assert torch.equal(hC, hC2)
 
 
 def test_bounded_wait_runs_out_and_the_stream_survives():
