@@ -98,6 +98,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, int c0, int c
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(m), "r"(c0), "r"(c1), "r"(src)
                : "memory");
 }
+// untiled form: `bytes` (a multiple of 16) from shared memory to any global address (16-byte aligned), this GPU's or
+// a peer's: a plain write as far as the other side is concerned
+__device__ __forceinline__ void bulk_store(void *dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all of this thread's bulk groups have finished READING shared memory (the source may be overwritten)
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

@@ -101,7 +101,7 @@ constexpr int OUT_TMA = 2;      // staged in shared memory, one cp.async.bulk.te
 // Gathering epilogue, cooperative form used by the epilogue warps.  A warp owns 32 weight columns (its TMEM lane
 // quadrant), so on its own it can only write 64 contiguous bytes per output row, and peer stores of that size reach
 // less than half of the NVLink rate.  The four epilogue warps therefore stage each 16-row chunk of the 128-column tile
-// in shared memory and write it out by rows: 256 contiguous bytes per row, 16 bytes per lane, every destination.
+// in shared memory and write it out by rows of 256 contiguous bytes, every destination.
 // Two slabs alternate; a warp may refill slab b for chunk c+2 once it has passed gfull[(c+1)&1], because every warp
 // reads chunk c before it arrives for chunk c+1.  Returns false when the (bounded) wait ran out.
 constexpr int GATHER_LD = TILE_N + 8;                       // slab row pitch in fp16 (272 bytes)
@@ -118,24 +118,24 @@ __device__ __forceinline__ bool store_chunk_gather4(const Params &p, const uint3
     if (!GROUPED) h = __hmul(h, sch);  // after the fp16 convert, as in the plain epilogue
     sb[i * GATHER_LD + quad * 32 + lane] = h;
   }
+  // The rows leave through the copy engine (cp.async.bulk, shared -> global, 256 bytes each): one lane per (row,
+  // destination) -- this warp's rows quad, quad + 4, quad + 8, quad + 12 times up to eight destinations -- so all of a
+  // chunk's rows are in flight at once and no thread waits for a peer's acknowledgement.  (Stores from registers,
+  // 8 or 16 bytes per lane, in any destination order, stayed at ~420 GB/s per GPU on eight GPUs.)
+  sm100::fence_proxy_async_smem();          // this thread's slab writes, for the async proxy that will read them
+  // every lane's earlier copies (previous chunk, other slab) have been read: passing this chunk's barrier frees that slab
+  sm100::tma_store_wait_read();
   __syncwarp();
   if (lane == 0) sm100::mbar_arrive(gfull_bar + 8 * buf);
   const bool ok = sm100::mbar_wait(gfull_bar + 8 * buf, (gcount >> 1) & 1, abort, p.wait_ns);
   ++gcount;
   if (!__all_sync(0xffffffffu, ok)) return false;
-  // 16 bytes per lane: a half-warp writes one 256-byte row, a warp instruction two rows; this warp's rows are
-  // quad, quad + 4, quad + 8, quad + 12
-  const size_t col = (size_t)p.c_col0 + n0 + (lane & 15) * 8;
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int r = quad + 4 * (2 * j + (lane >> 4)), mm = mrow0 + r;
-    const uint4 val = *reinterpret_cast<const uint4 *>(sb + r * GATHER_LD + (lane & 15) * 8);
-    if (mm < p.m) {
-      const size_t off = (size_t)mm * p.c_ld + col;
-      *reinterpret_cast<uint4 *>(p.C + off) = val;
-      for (int d = 0; d < p.n_extra; ++d) *reinterpret_cast<uint4 *>(p.C_extra[d] + off) = val;
-    }
+  const int r = quad + 4 * (lane & 3), dest = lane >> 2, mm = mrow0 + r;
+  if (dest <= p.n_extra && mm < p.m) {
+    __half *base = dest == 0 ? p.C : p.C_extra[dest - 1];
+    sm100::bulk_store(base + (size_t)mm * p.c_ld + p.c_col0 + n0, sm100::smem_u32(sb + r * GATHER_LD), TILE_N * 2);
   }
+  sm100::tma_store_commit();
   return true;
 }
 
@@ -634,6 +634,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__
     }
     // the TMA stores of this thread have left shared memory and reached C before the CTA ends (also after a give-up)
     if (OUT == OUT_TMA && quad == 0 && lane == 0) tma_store_wait_all();
+    if (OUT == OUT_GATHER) tma_store_wait_all();   // every lane issues row copies in the gathering form
   } else if (warp == PRODUCER_WARP) {
     // =========================================================== TMA producer (rest of the ring)
     // The whole warp runs the loop (warp-uniform operands); one elected lane issues.

@@ -364,6 +364,7 @@ w4a16_tc2_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant_
     }
     // the TMA stores of this thread have left shared memory and reached C before the CTA ends (also after a give-up)
     if (OUT == OUT_TMA && quad == 0 && lane == 0) tma_store_wait_all();
+    if (OUT == OUT_GATHER) tma_store_wait_all();   // every lane issues row copies in the gathering form
   } else if (warp == PRODUCER_WARP) {
     // =========================================================== TMA producer (one per CTA, each for its own halves)
     const int first = min(S, nsteps);

@@ -449,6 +449,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     }
     // the TMA stores of this thread have left shared memory and reached C before the CTA ends (also after a give-up)
     if (OUT == OUT_TMA && quad == 0 && lane == 0) tma_store_wait_all();
+    if (OUT == OUT_GATHER) tma_store_wait_all();   // every lane issues row copies in the gathering form
   } else if (warp == PRODUCER_WARP) {
     // =========================================================== TMA producer (rest of the ring)
     long long c_wait = 0, c_issue = 0;

@@ -81,6 +81,27 @@ def test_decode_sweep_g128(m, n, k):
     run_problem(m, n, k, groupsize=128, seed=m)
 
 
+@pytest.mark.parametrize("m,n,k,gs,form", [
+    (16, 2048, 4096, 128, "clusters of 8"), (5, 2048, 8192, -1, "clusters of 8"),
+    (16, 4096, 2048, 128, "clusters of 4"), (1, 4096, 11008 - 11008 % 256, -1, "clusters of 4, uneven k shares"),
+    (16, 8192, 1024, 128, "clusters of 2"), (9, 8192, 2048, -1, "clusters of 2"),
+    (16, 12288, 512, 128, "one whole tile per CTA"), (3, 12288, 1024, -1, "one whole tile per CTA"),
+    (16, 19200, 1024, 128, "stream-K, 150 tiles over 148 CTAs"), (16, 5120, 5120, 128, "stream-K, 40 tiles"),
+])
+def test_decode_kernel_forms(m, n, k, gs, form):
+    """Every way the m <= 16 kernel splits a layer on a whole B200: one cluster per tile with the partial tiles
+    reduced over distributed shared memory (2, 4 and 8 ranks, also with uneven k shares), one whole tile per CTA, and
+    stream-K with the fix-up through L2; group and per-channel scales.  Oracle on column windows for the wide ones."""
+    A, q, s = orc.make_problem(m, n, k, gs, seed=n + k + m)
+    At, Bt, st = pack_problem(A, q, s)
+    C = run_mul(At, Bt, st, m, n)
+    for n0 in sorted(set([0, (n // 2) // 256 * 256, n - 256])):
+        ref = orc.c_gemm(A, np.ascontiguousarray(q[:, n0:n0 + 256]), np.ascontiguousarray(s[:, n0:n0 + 256]), gs)
+        check(C[:, n0:n0 + 256], ref, "%s, window %d" % (form, n0))
+    C2 = run_mul(At, Bt, st, m, n)
+    assert torch.equal(C, C2), form     # the order of the additions is fixed in every form
+
+
 @pytest.mark.parametrize("sms", [1, 2, 3, 5, 7, 31, 64, 147, 148])
 def test_stream_k_split_counts(sms):
     """Every way of cutting tiles between CTAs, including CTAs that hold only a middle slice of one tile."""
