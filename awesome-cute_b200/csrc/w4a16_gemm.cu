@@ -372,8 +372,13 @@ int pick_cluster_size(int n_tiles, int k_iters, int nsm) {
   int best = 0;
   for (int cl = 2; cl <= 8; cl *= 2)
     if (n_tiles * cl <= nsm && k_iters >= 2 * cl) best = cl;
-  if (!best || 10 * n_tiles * best < 6 * nsm || k_iters > 32 * best) return 0;
-  return best;
+  if (!best || k_iters > 32 * best) return 0;
+  if (10 * n_tiles * best >= 6 * nsm) return best;
+  // Very few tiles (a narrow column shard of a deep layer: 1024 x 28672 is 8 tiles of 112 stages): even clusters of 8
+  // leave SMs idle, but stream-K would cut every tile 16 ways and its finisher would then fold fifteen slices
+  // through L2, five polls one after the other.  Measured at m = 16: 1024 x 28672 11.5 us on 8 clusters of 8 against
+  // 14.7 us on stream-K, 1024 x 8192 7.5 against 12.2 us.
+  return (best == 8 && 4 * n_tiles * best >= nsm) ? best : 0;
 }
 
 // Returns -2 when the clusters cannot all be resident at once on this device (the caller takes the stream-K form).
