@@ -625,10 +625,13 @@ int dispatch_tc(const Problem &pr) {
   if (pr.m <= 16 && k256 && g_use_decode) {   // the HBM-bound case has a kernel of its own
     // few tiles and no split count from the caller: one cluster per tile
     if (g_use_cluster && pr.sms <= 0 && pr.c_ld == 0 && !pr.orphan_finisher) {
-      const int cl = pick_cluster_size(pr.n / w4a16::TILE_N, pr.k / 256, sm_count(pr.dev));
-      if (cl) {
+      const int n_tiles = pr.n / w4a16::TILE_N, nsm = sm_count(pr.dev);
+      // the size that fills most SMs; if that many clusters of that size cannot be resident together (a cluster
+      // lives inside one GPC), half the size, as long as a quarter of the SMs still gets work
+      for (int cl = pick_cluster_size(n_tiles, pr.k / 256, nsm); cl >= 2; cl /= 2) {
         const int rc = launch_decode_cluster_g(pr, cl);
         if (rc != -2) return rc;
+        if (4 * n_tiles * (cl / 2) < nsm || pr.k / 256 > 32 * (cl / 2)) break;
       }
     }
     return launch_decode_g(pr);
