@@ -627,11 +627,13 @@ int dispatch_tc(const Problem &pr) {
     if (g_use_cluster && pr.sms <= 0 && pr.c_ld == 0 && !pr.orphan_finisher) {
       const int n_tiles = pr.n / w4a16::TILE_N, nsm = sm_count(pr.dev);
       // the size that fills most SMs; if that many clusters of that size cannot be resident together (a cluster
-      // lives inside one GPC), half the size, as long as a quarter of the SMs still gets work
+      // lives inside one GPC), half the size, as long as a quarter of the SMs still gets work and a rank no more than
+      // 16 stages (2048 x 8192 at m = 16: 7.5 us on 16 clusters of 4 against 9.7 us on stream-K; 2048 x 28672 with 28
+      // stages per rank: 15.7 against 14.8 us, so that one stays on stream-K)
       for (int cl = pick_cluster_size(n_tiles, pr.k / 256, nsm); cl >= 2; cl /= 2) {
         const int rc = launch_decode_cluster_g(pr, cl);
         if (rc != -2) return rc;
-        if (4 * n_tiles * (cl / 2) < nsm || pr.k / 256 > 32 * (cl / 2)) break;
+        if (4 * n_tiles * (cl / 2) < nsm || pr.k / 256 > 16 * (cl / 2)) break;
       }
     }
     return launch_decode_g(pr);
