@@ -735,6 +735,8 @@ def run_case(args):
     dev = torch.device("cuda", 0)
     gen = torch.Generator(device=dev).manual_seed(7)
     copies = max(2, min(8, int(300e6 // (n * k // 2)) + 1))     # rotate through > 2 x L2 of weights
+    if args.copies > 0:
+        copies = args.copies                                     # (1: the weights stay in L2, the bound of any prefetch)
     Bs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen) for _ in range(copies)]
     groups = 1 if g == -1 else k // g
     ss = [(torch.rand((groups, n), device=dev, generator=gen) * 0.015 + 0.005).half() for _ in range(copies)]
@@ -807,6 +809,8 @@ def main():
     ap.add_argument("--no-sharded", action="store_true", help="skip the column-sharded 70B configuration")
     ap.add_argument("--case", default=None, help="NxKxM[xG]: time one shape only (graph replay; --eager for profilers)")
     ap.add_argument("--eager", action="store_true", help="with --case: plain launches instead of a CUDA graph")
+    ap.add_argument("--copies", type=int, default=0,
+                    help="with --case: weight copies the launches rotate through (default: enough for > 2 x L2; 1 keeps the weights in L2)")
     ap.add_argument("--workload", default="decode7b", choices=["decode7b", "sharded70b"],
                     help="decode7b: the headline step; sharded70b: only the Llama-2-70B layers column-sharded over the ranks")
     args = ap.parse_args()
