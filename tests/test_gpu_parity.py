@@ -180,6 +180,22 @@ def test_golden_from_reference_packer(golden_dir):
         check(C, g["C_ref32"], os.path.basename(path))
 
 
+@pytest.mark.parametrize("name", ["big_g128_m16_n2048_k4096", "big_gm1_m16_n1024_k2048"])
+def test_big_golden_against_reference_product(golden_dir, name):
+    """The layer-sized golden cases through the kernel: operands packed by the shipped packer (whose output matches
+    the reference packer's by digest, tests/test_packer.py), result against the REFERENCE's own fp32 product stored
+    in the fixture.  2048 x 4096 g128 takes the cluster form of the m <= 16 kernel, 1024 x 2048 per-channel too."""
+    from test_oracle import big_operands
+    g, A, w, _ = big_operands(golden_dir, name)
+    gs, s = int(g["groupsize"]), g["s"]
+    m, n = int(g["m"]), int(g["n"])
+    q = orc.c_quantize(w, s, gs)
+    At, Bt, st = pack_problem(A, q, s)
+    for sms in (-1, 37):
+        C = run_mul(At, Bt, st, m, n, sms=sms)
+        check(C, g["C_ref32"], "%s sms=%d" % (name, sms))
+
+
 def test_linearity_at_full_size():
     """Size-independent property at a benchmark shape: GEMM(a1 + a2) == GEMM(a1) + GEMM(a2) up to fp16
     rounding of the three outputs."""

@@ -78,6 +78,47 @@ def test_gemm_matches_reference_matmul(golden_dir, name):
         assert ok, (err, bound)
 
 
+BIG = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "big_*.npz")))
+
+
+def big_operands(golden_dir, name):
+    """A layer-sized golden case: operands regenerated from tests/golden/synth.py, the reference's scales and fp32
+    product from the fixture, its other results as SHA-256 digests."""
+    import hashlib
+    import sys
+    sys.path.insert(0, golden_dir)
+    from synth import synth_fp16
+    g = dict(np.load(os.path.join(golden_dir, name + ".npz")))
+    m, n, k, seed = int(g["m"]), int(g["n"]), int(g["k"]), int(g["seed"])
+    sha = lambda x: hashlib.sha256(np.ascontiguousarray(x).tobytes()).hexdigest()
+    return g, synth_fp16(m, k, seed + 1000), synth_fp16(k, n, seed), sha
+
+
+def test_big_cases_present():
+    assert len(BIG) == 2
+
+
+@pytest.mark.parametrize("name", BIG)
+def test_big_case_every_stage_matches_reference(golden_dir, name):
+    """2048 x 4096 g128 and 1024 x 2048 per-channel through every step of the reference's pipeline
+    (marlin_test.py:18-55, marlin.py:92-131): codes, fake-quantised weights, packed words, permuted scales bit-exact
+    (by digest), the product to fp32 rounding noise."""
+    g, A, w, sha = big_operands(golden_dir, name)
+    gs = int(g["groupsize"])
+    s = g["s"]
+    for quant, deq, pack, perm in ((orc.np_quantize, orc.np_dequant, orc.np_pack_weights, orc.np_permute_scales),
+                                   (orc.c_quantize, orc.c_dequant, orc.c_pack_weights, orc.c_permute_scales)):
+        q = quant(w, s, gs)
+        assert sha(q) == str(g["sha_q"])
+        assert sha(deq(q, s, gs)) == str(g["sha_ref"])
+        assert sha(pack(q)) == str(g["sha_B"])
+        assert sha(perm(s)) == str(g["sha_s_packed"])
+    want = g["C_ref32"]
+    q = orc.c_quantize(w, s, gs)
+    for C in (orc.c_gemm(A, q, s, gs), orc.c_gemm_packed(A, orc.c_pack_weights(q), orc.c_permute_scales(s), gs)):
+        assert np.max(np.abs(C - want)) <= 1e-5 * np.max(np.abs(want))
+
+
 def test_gemm_edge_shapes():
     # empty problems return zeros without touching memory (marlin_cute_kernel.cu:59-60)
     A, q, s = orc.make_problem(0, 256, 128, 128, 0)

@@ -37,6 +37,21 @@ def test_quantize_pack_is_layer_pack(golden_dir, name):
     assert np.array_equal(sp.view(np.uint16), g["s_packed"].view(np.uint16))
 
 
+@pytest.mark.parametrize("name", ["big_g128_m16_n2048_k4096", "big_gm1_m16_n1024_k2048"])
+def test_big_case_shipped_packer_matches_reference(golden_dir, name):
+    """The layer-sized golden cases through the shipped packer: the reference's packed words and permuted scales by
+    digest, from the fake-quantised weights as Layer.pack gets them and from the codes."""
+    from test_oracle import big_operands
+    g, _, w, sha = big_operands(golden_dir, name)
+    gs, s = int(g["groupsize"]), g["s"]
+    q = orc.c_quantize(w, s, gs)
+    assert sha(pkg.pack_weights(q)) == str(g["sha_B"])
+    assert sha(pkg.permute_scales(s)) == str(g["sha_s_packed"])
+    B, sp = pkg.quantize_pack(np.ascontiguousarray(orc.c_dequant(q, s, gs).T), s, gs)
+    assert sha(B) == str(g["sha_B"])
+    assert sha(sp) == str(g["sha_s_packed"])
+
+
 @pytest.mark.parametrize("k,n,groups", [(16, 64, 1), (128, 256, 1), (256, 4096, 2), (1024, 704, 8), (4096, 128, 32)])
 def test_pack_matches_oracle_random(k, n, groups):
     rng = np.random.default_rng(k * 31 + n)
