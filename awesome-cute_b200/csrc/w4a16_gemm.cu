@@ -665,11 +665,20 @@ int dispatch_tc(const Problem &pr) {
   // The pair kernel runs a ragged last tile at its own width (UMMA N = its rows rounded up to 16), so padding costs
   // nothing there; what a narrow tile still costs is its dequantisation, about 0.55 of a full 192-row tile's time.
   // A full 128-row tile takes about 0.72 of a 192-row tile's time.
+  // (a ragged tile of exactly 128 rows inside the 192-row kernel measured 1-2 % behind the 128-row kernel, which has
+  // four operand buffers in tensor memory instead of two: its cost is taken as 0.73)
   auto pair_cost = [&](int t, double full_cost) {
-    const int rem = pr.m % t;
-    return (pr.m / t) * full_cost + (rem ? std::max(((rem + 15) & ~15) / 192.0, 0.55) : 0.0);
+    const int rem = pr.m % t, rows = (rem + 15) & ~15;
+    const double ragged = rows <= 128 ? std::max(0.73 * rows / 128.0, 0.55) : 0.73 + 0.27 * (rows - 128) / 64.0;
+    return (pr.m / t) * full_cost + (rem ? ragged : 0.0);
   };
-  const long tm = pair_cost(192, 1.0) <= pair_cost(128, 0.72) ? 192 : 128;
+  // W4A16_FORCE_TM=128 / 192 in the environment fixes the batch tile of the large-batch kernels (A/B timing)
+  static const int force_tm = [] {
+    const char *e = std::getenv("W4A16_FORCE_TM");
+    const int v = e ? atoi(e) : 0;
+    return (v == 128 || v == 192) ? v : 0;
+  }();
+  const long tm = force_tm ? force_tm : (pair_cost(192, 1.0) < pair_cost(128, 0.72) ? 192 : 128);   // (a tie: a batch below 128 rows is one ragged tile either way)
   // (an explicit split count from the caller stands in for the 74 pairs of a whole B200)
   const long pair_stages = (long)(pr.n / 256) * ((pr.m + tm - 1) / tm) * (pr.k / 128) / (pr.sms > 1 ? pr.sms / 2 : 74);
   if (g_use_pairs && k128 && pr.n % 256 == 0 && pair_stages >= 32 && !pr.fixed_partials && !pr.orphan_finisher) {
