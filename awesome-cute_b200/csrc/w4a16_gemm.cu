@@ -292,6 +292,26 @@ const bool g_aligned_cut = [] {
   return !(e && e[0] == '0');
 }();
 
+// How many workers (CTAs, or CTA pairs) a problem of `tiles` tiles x `k_iters` stages gets when it has fewer tiles than
+// workers and batch tiles wider than 16 rows.  The even cut over all workers makes most of them straddle two tiles
+// (contributor to one, finisher of the other) and cuts a tile workers / tiles ways; a cut that lines up with the
+// tiles (every tile cut the same s ways, s a divisor of k_iters, every worker inside one tile) avoids the straddling,
+// and a finisher then folds s - 1 partial tiles through L2.  Both are priced in microseconds, t_stage per stage and
+// t_fix per partial tile folded, and the cheaper one wins.  Measured at m = 128 (single-CTA kernel): 4096 x 4096
+// 17.5 -> 14.9 us (s = 4), 1024 x 4096 27.8 us on the even cut (every tile cut 16 ways).
+int pick_workers(int tiles, int k_iters, int max_workers, double t_stage, double t_fix) {
+  const long total = (long)tiles * k_iters;
+  const int even_per = (int)((total + max_workers - 1) / max_workers);
+  double best = even_per * t_stage + ((double)max_workers / tiles + 1.0) * t_fix;
+  int workers = max_workers;
+  for (int s = 1; s <= k_iters && (long)tiles * s <= max_workers; ++s) {
+    if (k_iters % s) continue;
+    const double cost = (k_iters / s) * t_stage + (s - 1) * t_fix;
+    if (cost < best) best = cost, workers = tiles * s;
+  }
+  return workers;
+}
+
 // One CTA per SM, persistent, stream-K over (128-column tile, k-stage).
 template <class K>
 int launch_single(const Problem &pr) {
@@ -320,20 +340,10 @@ int launch_single(const Problem &pr) {
   const int tiles = p.n_tiles * p.m_tiles;
   if (pr.sms <= 0 && K::TM <= 16 && !pr.orphan_finisher && tiles <= grid && 100 * tiles >= 58 * grid) grid = tiles;
   if (grid > p.total_iters) grid = p.total_iters;
-  // Wider batch tiles, few tiles: a cut whose ranges line up with the tiles (every tile cut the same s ways, s a
-  // divisor of its stage count, every CTA inside one tile) beats the even cut over all SMs, whose CTAs straddle two
-  // tiles, contribute to one and finish the other, as long as it does not cost a CTA more than about eight extra
-  // stages (m = 128: 4096 x 4096 17.5 -> 15.0 us on 128 CTAs, 8192 x 8192 26.4 -> 21.6 us, 4096 x 4096 at m = 256
-  // 18.4 -> 16.5 us; 12288 x 4096, where the aligned cut is one whole tile per CTA and 11 stages more, stays).
-  if (pr.sms <= 0 && K::TM > 16 && g_aligned_cut && !pr.orphan_finisher && tiles <= grid) {
-    int s_best = 0;
-    for (int s = 1; s <= p.k_iters && (long)tiles * s <= grid; ++s)
-      if (p.k_iters % s == 0) s_best = s;
-    if (s_best > 0) {
-      const int even = (p.total_iters + grid - 1) / grid;
-      if (p.k_iters / s_best - even <= 8) grid = tiles * s_best;
-    }
-  }
+  // wider batch tiles, fewer tiles than SMs: see pick_workers (a partial tile of 128+ rows costs ~1.2 us to fold, one
+  // of 32-64 rows ~0.5 us)
+  if (pr.sms <= 0 && K::TM > 16 && g_aligned_cut && !pr.orphan_finisher && tiles <= grid)
+    grid = pick_workers(tiles, p.k_iters, grid, 0.45, K::TM >= 128 ? 1.2 : 0.5);
   p.iters_per_cta = (p.total_iters + grid - 1) / grid;
   grid = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
   p.s = static_cast<const __half *>(pr.s);
@@ -586,6 +596,22 @@ int launch_tc2(const Problem &pr) {
     p.total_iters = (tiles - p.sk_tile0) * p.k_iters;
     p.m_fast = pick_tile_order(pr.dev, 2.0 * pr.m * pr.k, 0.5 * pr.n * pr.k, p.n_tiles, p.m_tiles, pairs);
   }
+  // No whole-tile waves (fewer than two tiles per pair).  Fewer tiles than pairs: as in the single-CTA kernel
+  // (pick_workers).  More: a cut in which every pair takes a whole number of half tiles (cuts at tile edges and
+  // midpoints only) beats the even cut over all pairs when it costs a pair at most about eight more stages
+  // (4096 x 4096 at m = 1024 on 64 pairs of one and a half tiles each: 34.5 -> 32.7 us).
+  if (p.dp_waves == 0 && g_aligned_cut && pr.sms <= 0 && p.total_iters > 0) {
+    if (tiles <= pairs) {
+      pairs = pick_workers(tiles, p.k_iters, pairs, 0.45, TM >= 128 ? 1.2 : 0.5);
+    } else if (p.k_iters % 2 == 0) {
+      const int even = (p.total_iters + pairs - 1) / pairs;
+      for (int c = pairs; c >= 1 && 5 * c >= 3 * pairs; --c) {
+        if (p.total_iters % c || (p.total_iters / c) % (p.k_iters / 2)) continue;
+        if (p.total_iters / c - even <= 8) pairs = c;
+        break;
+      }
+    }
+  }
   p.iters_per_cta = p.total_iters > 0 ? (p.total_iters + pairs - 1) / pairs : 1;     // per PAIR
   if (p.dp_waves == 0) pairs = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
   p.workers = pairs;
@@ -680,8 +706,11 @@ int dispatch_tc(const Problem &pr) {
   // Large batches run on CTA pairs (two SMs per 256-column tile, half the activation traffic per SM): +16 % to +43 %
   // over the single-CTA kernel on B200.  192-row tiles beat 128-row tiles by ~8 % there, 12 % on the single-CTA
   // kernel: take them unless their row padding costs more than that.
-  // ... when each pair gets at least ~32 k-stages: on smaller problems the single-CTA kernel's shorter start-up and
-  // fix-up win (4096 x 4096 at m = 128: 17.5 us against 25.7 us)
+  // ... when each pair gets at least ~6 k-stages.  (With the even cut over all pairs the threshold was 32: a few
+  // large tiles cut five ways with straddling pairs lost to the single-CTA kernel, 4096 x 4096 at m = 128 25.7 against
+  // 17.5 us.  With the cut lined up with the tiles the pairs win down to here: the same problem 14.2 us on pairs,
+  // 14.9 us on single CTAs; 4096 x 4096 at m = 96 12.2 against 14.8 us, at m = 256 15.0 against 16.3 us, 8192 x 8192 at
+  // m = 128 21.5 against 24.8 us.)
   // The pair kernel runs a ragged last tile at its own width (UMMA N = its rows rounded up to 16), so padding costs
   // nothing there; what a narrow tile still costs is its dequantisation, about 0.55 of a full 192-row tile's time.
   // A full 128-row tile takes about 0.72 of a 192-row tile's time.
@@ -701,7 +730,9 @@ int dispatch_tc(const Problem &pr) {
   const long tm = force_tm ? force_tm : (pair_cost(192, 1.0) < pair_cost(128, 0.72) ? 192 : 128);   // (a tie: a batch below 128 rows is one ragged tile either way)
   // (an explicit split count from the caller stands in for the 74 pairs of a whole B200)
   const long pair_stages = (long)(pr.n / 256) * ((pr.m + tm - 1) / tm) * (pr.k / 128) / (pr.sms > 1 ? pr.sms / 2 : 74);
-  if (g_use_pairs && k128 && pr.n % 256 == 0 && pair_stages >= 32 && !pr.fixed_partials && !pr.orphan_finisher) {
+  // (W4A16_PAIR_MIN_STAGES in the environment moves the threshold: A/B timing)
+  static const int pair_min = [] { const char *e = std::getenv("W4A16_PAIR_MIN_STAGES"); return e ? atoi(e) : 6; }();
+  if (g_use_pairs && k128 && pr.n % 256 == 0 && pair_stages >= pair_min && !pr.fixed_partials && !pr.orphan_finisher) {
     int rc;
     if (tm == 192)
       rc = launch_tc2_g<192, 128>(pr);
