@@ -590,6 +590,18 @@ int launch_tc2(const Problem &pr) {
   // With two or more tiles per pair, all but the last one or two are taken whole and round-robin (tiles in flight at
   // one time are neighbours and share their operands in L2); the rest is split by k-stages as before.
   const int tiles = p.n_tiles * p.m_tiles;
+  // A slightly smaller number of pairs that divides the tile count leaves no stream-K part at all (no partial tiles,
+  // no straddling): taken when its waves cost fewer stages than the waves plus the stream-K share plus about eight
+  // stages' worth of fix-up (12288 x 4096 at m = 1024: 288 tiles = 4 waves of 72 pairs, 81.2 -> 77.1 us).
+  if (g_use_waves && g_aligned_cut && pr.sms <= 0 && tiles >= 2 * pairs && tiles % pairs != 0) {
+    const int waves = tiles / pairs - 1;
+    const long with_sk = (long)waves * p.k_iters + ((long)(tiles - waves * pairs) * p.k_iters + pairs - 1) / pairs + 8;
+    for (int c = pairs - 1; 100 * c >= 93 * pairs; --c)
+      if (tiles % c == 0 && (long)(tiles / c) * p.k_iters < with_sk) {
+        pairs = c;
+        break;
+      }
+  }
   if (g_use_waves && tiles >= 2 * pairs) {
     p.dp_waves = tiles % pairs == 0 ? tiles / pairs : tiles / pairs - 1;
     p.sk_tile0 = p.dp_waves * pairs;
