@@ -298,11 +298,14 @@ const bool g_aligned_cut = [] {
 // tiles (every tile cut the same s ways, s a divisor of k_iters, every worker inside one tile) avoids the straddling,
 // and a finisher then folds s - 1 partial tiles through L2.  Both are priced in microseconds, t_stage per stage and
 // t_fix per partial tile folded, and the cheaper one wins.  Measured at m = 128 (single-CTA kernel): 4096 x 4096
-// 17.5 -> 14.9 us (s = 4), 1024 x 4096 27.8 us on the even cut (every tile cut 16 ways).
+// 17.5 -> 14.9 us (s = 4), 1024 x 4096 27.8 us on the even cut (every tile cut 16 ways).  The two prices were fitted on
+// CTA pairs at m = 128 (us per launch): 2048 x 8192 cut 2 / 4 / 8 ways 19.2 / 16.5 / 19.3, 1024 x 28672 cut 4 / 7 / 8 / 16
+// ways 31.6 / 26.3 / 26.9 / 33.3, 4096 x 4096 cut 2 / 4 ways 13.5 / 14.3, 12288 x 4096 whole tiles on 48 pairs 20.7
+// against 18.8 on the even cut over 74.
 int pick_workers(int tiles, int k_iters, int max_workers, double t_stage, double t_fix) {
   const long total = (long)tiles * k_iters;
   const int even_per = (int)((total + max_workers - 1) / max_workers);
-  double best = even_per * t_stage + ((double)max_workers / tiles + 1.0) * t_fix;
+  double best = even_per * t_stage + ((double)max_workers / tiles) * t_fix;
   int workers = max_workers;
   for (int s = 1; s <= k_iters && (long)tiles * s <= max_workers; ++s) {
     if (k_iters % s) continue;
@@ -340,10 +343,10 @@ int launch_single(const Problem &pr) {
   const int tiles = p.n_tiles * p.m_tiles;
   if (pr.sms <= 0 && K::TM <= 16 && !pr.orphan_finisher && tiles <= grid && 100 * tiles >= 58 * grid) grid = tiles;
   if (grid > p.total_iters) grid = p.total_iters;
-  // wider batch tiles, fewer tiles than SMs: see pick_workers (a partial tile of 128+ rows costs ~1.2 us to fold, one
+  // wider batch tiles, fewer tiles than SMs: see pick_workers (a partial tile of 128+ rows costs ~2.2 us to fold, one
   // of 32-64 rows ~0.5 us)
   if (pr.sms <= 0 && K::TM > 16 && g_aligned_cut && !pr.orphan_finisher && tiles <= grid)
-    grid = pick_workers(tiles, p.k_iters, grid, 0.45, K::TM >= 128 ? 1.2 : 0.5);
+    grid = pick_workers(tiles, p.k_iters, grid, 0.45, K::TM >= 128 ? 2.2 : 0.5);
   p.iters_per_cta = (p.total_iters + grid - 1) / grid;
   grid = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
   p.s = static_cast<const __half *>(pr.s);
@@ -614,7 +617,7 @@ int launch_tc2(const Problem &pr) {
   // (4096 x 4096 at m = 1024 on 64 pairs of one and a half tiles each: 34.5 -> 32.7 us).
   if (p.dp_waves == 0 && g_aligned_cut && pr.sms <= 0 && p.total_iters > 0) {
     if (tiles <= pairs) {
-      pairs = pick_workers(tiles, p.k_iters, pairs, 0.45, TM >= 128 ? 1.2 : 0.5);
+      pairs = pick_workers(tiles, p.k_iters, pairs, 0.45, TM >= 128 ? 2.2 : 0.5);
     } else if (p.k_iters % 2 == 0) {
       const int even = (p.total_iters + pairs - 1) / pairs;
       for (int c = pairs; c >= 1 && 5 * c >= 3 * pairs; --c) {
@@ -741,7 +744,12 @@ int dispatch_tc(const Problem &pr) {
   }();
   const long tm = force_tm ? force_tm : (pair_cost(192, 1.0) < pair_cost(128, 0.72) ? 192 : 128);   // (a tie: a batch below 128 rows is one ragged tile either way)
   // (an explicit split count from the caller stands in for the 74 pairs of a whole B200)
-  const long pair_stages = (long)(pr.n / 256) * ((pr.m + tm - 1) / tm) * (pr.k / 128) / (pr.sms > 1 ? pr.sms / 2 : 74);
+  // (fewer tiles than pairs: the pairs that pick_workers would put to work)
+  const int pair_tiles = (int)((pr.n / 256) * ((pr.m + tm - 1) / tm));
+  int pairs_at_work = pr.sms > 1 ? pr.sms / 2 : 74;
+  if (pr.sms <= 0 && g_aligned_cut && pr.n % 256 == 0 && k128 && pair_tiles <= pairs_at_work)
+    pairs_at_work = pick_workers(pair_tiles, pr.k / 128, pairs_at_work, 0.45, 2.2);
+  const long pair_stages = (long)pair_tiles * (pr.k / 128) / pairs_at_work;
   // (W4A16_PAIR_MIN_STAGES in the environment moves the threshold: A/B timing)
   static const int pair_min = [] { const char *e = std::getenv("W4A16_PAIR_MIN_STAGES"); return e ? atoi(e) : 6; }();
   if (g_use_pairs && k128 && pr.n % 256 == 0 && pair_stages >= pair_min && !pr.fixed_partials && !pr.orphan_finisher) {
