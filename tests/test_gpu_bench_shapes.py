@@ -79,3 +79,27 @@ def test_llama70b_layers_and_their_shards(n_full, k):
             del C
         del Bt, st
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("m,n,k,what", [
+    (128, 1024, 4096, "4 pair tiles cut 2 ways: 8 pairs, each inside one tile"),
+    (128, 2048, 8192, "8 pair tiles cut 4 ways"),
+    (96, 4096, 4096, "16 pair tiles of one ragged batch tile"),
+    (128, 512, 4096, "too few stages per pair: single-CTA kernel, 4 tiles cut evenly"),
+    (256, 4096, 4096, "two batch tiles of 128 rows, 64 pairs"),
+    (576, 12288, 4096, "144 tiles = 2 whole waves on 72 of the 74 pairs, no stream-K part"),
+    (200, 4096, 11008, "stage count without a usable divisor: the even cut"),
+])
+def test_worker_counts_of_few_wide_tiles(m, n, k, what):
+    """Batches of 65+ rows on layers with fewer tiles than workers: the launcher prices the even cut against cuts that
+    line up with the tiles and takes a worker count of its own (fewer CTAs or CTA pairs than the device has).  Each of
+    these takes a different branch of that choice; the 1024-row cases are in test_prefill_llama7b_shapes."""
+    A, q, s = orc.make_problem(m, n, k, GS, seed=m + n + k)
+    Bt, st = to_dev(pkg.pack_weights(q)), to_dev(pkg.permute_scales(s))
+    C = run_mul(to_dev(A), Bt, st, m, n)
+    rows = _rows(m)
+    A_sub = np.ascontiguousarray(A[rows])
+    rows_t = torch.from_numpy(rows).to(C.device)
+    for w0 in _windows(n):
+        ref = orc.c_gemm(A_sub, np.ascontiguousarray(q[:, w0:w0 + 256]), np.ascontiguousarray(s[:, w0:w0 + 256]), GS)
+        check(C[rows_t][:, w0:w0 + 256], ref, "%s (m=%d n=%d k=%d) window %d" % (what, m, n, k, w0))
