@@ -23,6 +23,7 @@ SYMBOLS = {
     "w4a16_workspace_ints": (_i, [_i, _i]),
     "w4a16_device_status": (_i, [_i, _vp]),
     "w4a16_release_stream": (_i, [_i, _vp]),
+    "w4a16_plan": (_i, [_i, _i, _i, _i, _i, _i, _vp]),
     "w4a16_selftest_unanswered_wait": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i]),
     "w4a16_last_cuda_error": (ctypes.c_char_p, []),
     "w4a16_pack_weights": (_i, [_vp, _i, _i, _vp]),
@@ -58,6 +59,25 @@ def _load():
 
 
 lib = _load()
+
+
+class Plan(ctypes.Structure):
+    """w4a16_plan_t of include/w4a16.h"""
+    _fields_ = [(n, _i) for n in ("kernel", "tile_rows", "k_per_stage", "workers", "ctas_per_worker", "whole_tile_waves",
+                                  "stages_per_worker")]
+
+
+KERNEL_NAMES = {0: "none", 1: "single", 2: "pairs", 3: "decode", 4: "decode_cluster"}
+
+
+def plan(m, n, k, groupsize=128, sms=-1, device_sms=148):
+    """Which kernel `mul` would launch for these sizes on a device of `device_sms` SMs and how the work is cut
+    (w4a16_plan: host arithmetic only, works without a GPU).  Returns (return code, dict)."""
+    out = Plan()
+    rc = lib.w4a16_plan(m, n, k, groupsize, sms, device_sms, ctypes.byref(out))
+    d = {f: getattr(out, f) for f, _ in Plan._fields_}
+    d["kernel"] = KERNEL_NAMES.get(d["kernel"], d["kernel"])
+    return rc, d
 
 
 def last_cuda_error():

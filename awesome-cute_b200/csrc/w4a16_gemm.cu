@@ -164,7 +164,15 @@ struct Problem {
   // tile also goes to the same place of n_extra further buffers
   int c_ld = 0, c_col0 = 0, n_extra = 0;
   void *const *C_extra = nullptr;   // device table of the n_extra further buffers
+  // set only by w4a16_plan: describe the launch instead of making it (no CUDA call on that path)
+  w4a16_plan_t *plan = nullptr;
+  int plan_sms = 0;                 // SMs of the device the plan is for
 };
+
+// SMs of the problem's device: asked of CUDA, or given by the caller of w4a16_plan
+int problem_sm_count(const Problem &pr);
+
+int problem_sm_count(const Problem &pr) { return pr.plan ? pr.plan_sms : sm_count(pr.dev); }
 
 void set_output(w4a16::Params &p, const Problem &pr) {
   p.C = static_cast<__half *>(pr.C);
@@ -276,6 +284,7 @@ struct GeneralKernel {
   using Cfg = w4a16::Config<TM_, KS_, OUT_>;
   static constexpr int TM = TM_, KS = KS_, THREADS = Cfg::THREADS, SMEM = Cfg::SMEM_BYTES, OUT = OUT_;
   static constexpr bool GROUPED = GROUPED_;
+  static constexpr bool IS_DECODE = false;
   static auto kernel() { return w4a16::w4a16_tc_kernel<TM_, KS_, GROUPED_, OUT_>; }
 };
 template <bool GROUPED_, int OUT_>
@@ -283,6 +292,7 @@ struct DecodeKernel {
   using Cfg = w4a16::DecodeConfig<OUT_>;
   static constexpr int TM = Cfg::TM, KS = Cfg::KS, THREADS = Cfg::THREADS, SMEM = Cfg::SMEM_BYTES, OUT = OUT_;
   static constexpr bool GROUPED = GROUPED_;
+  static constexpr bool IS_DECODE = true;
   static auto kernel() { return w4a16::w4a16_decode_kernel<GROUPED_, OUT_>; }
 };
 
@@ -323,7 +333,7 @@ int launch_single(const Problem &pr) {
   constexpr int smem = K::SMEM > 116 * 1024 ? K::SMEM : 116 * 1024;
   static bool attr_done[64] = {false};
 
-  const int nsm = sm_count(pr.dev);
+  const int nsm = problem_sm_count(pr);
   if (nsm <= 0) return W4A16_ERR_CUDA;
 
   w4a16::Params p{};
@@ -358,6 +368,10 @@ int launch_single(const Problem &pr) {
     grid = 1;                          // ... and only the CTA that finishes it is launched
   }
 
+  if (pr.plan) {
+    *pr.plan = w4a16_plan_t{K::IS_DECODE ? W4A16_KERNEL_DECODE : W4A16_KERNEL_SINGLE, K::TM, K::KS, grid, 1, 0, p.iters_per_cta};
+    return W4A16_OK;
+  }
   Maps mp;
   if (!get_maps(pr, K::KS, K::TM, K::GROUPED, K::OUT == w4a16::OUT_TMA, mp)) return W4A16_ERR_CUDA;
   p.a_box3d = mp.a_box3d;
@@ -423,8 +437,13 @@ int launch_decode_cluster(const Problem &pr) {
   static bool attr_done[64] = {false};
   static int max_clusters[64] = {0};
 
-  const int nsm = sm_count(pr.dev);
+  const int nsm = problem_sm_count(pr);
   if (nsm <= 0) return W4A16_ERR_CUDA;
+  if (pr.plan) {   // (as if every cluster of this size could be resident: a cluster lives inside one GPC)
+    if (nsm / CL < pr.n / w4a16::TILE_N) return -2;
+    *pr.plan = w4a16_plan_t{W4A16_KERNEL_DECODE_CLUSTER, Cfg::TM, Cfg::KS, pr.n / w4a16::TILE_N * CL, CL, 0, pr.k / Cfg::KS / CL};
+    return W4A16_OK;
+  }
   w4a16::Params p{};
   p.m = pr.m, p.n = pr.n, p.k = pr.k;
   p.n_tiles = pr.n / w4a16::TILE_N;
@@ -522,7 +541,7 @@ const int g_m_fast = [] {
 // the other way round.  Whatever exceeds ~5/8 of L2 is taken to miss in proportion.  Returns 1 for batch-first.
 int pick_tile_order(int dev, double act_bytes, double weight_bytes, int n_tiles, int m_tiles, int pairs) {
   if (g_m_fast >= 0) return g_m_fast;
-  const double cap = 0.625 * (double)l2_bytes(dev);
+  const double cap = 0.625 * (dev < 0 ? 126.0 * 1024 * 1024 : (double)l2_bytes(dev));   // (dev < 0: w4a16_plan, a B200's L2)
   const double waves = (double)n_tiles * m_tiles / pairs;
   auto traffic = [&](double bytes, double passes) {
     const double miss = bytes <= cap ? 0.0 : 1.0 - cap / bytes;
@@ -541,7 +560,7 @@ int launch_tc2(const Problem &pr) {
   static bool attr_done[64] = {false};
   static int max_pairs[64] = {0};
 
-  const int nsm = sm_count(pr.dev);
+  const int nsm = problem_sm_count(pr);
   if (nsm <= 0) return W4A16_ERR_CUDA;
 
   w4a16::Params p{};
@@ -571,7 +590,7 @@ int launch_tc2(const Problem &pr) {
   cfg.attrs = attr;
   cfg.numAttrs = 2;
 
-  {
+  if (!pr.plan) {
     std::lock_guard<std::mutex> lock(g_mu);
     if (!attr_done[pr.dev]) {
       if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"))
@@ -584,10 +603,11 @@ int launch_tc2(const Problem &pr) {
       attr_done[pr.dev] = true;
     }
   }
-  if (max_pairs[pr.dev] < 1) return -2;   // no CTA pair can be scheduled here: the caller takes the single-CTA kernel
+  const int fit_pairs = pr.plan ? nsm / 2 : max_pairs[pr.dev];
+  if (fit_pairs < 1) return -2;   // no CTA pair can be scheduled here: the caller takes the single-CTA kernel
   int pairs = pr.sms > 0 ? pr.sms / 2 : nsm / 2;
   if (pairs < 1) pairs = 1;
-  if (pairs > max_pairs[pr.dev]) pairs = max_pairs[pr.dev];
+  if (pairs > fit_pairs) pairs = fit_pairs;
   if (pairs > MAX_GRID / 2) pairs = MAX_GRID / 2;
   if (pairs > p.total_iters) pairs = p.total_iters;
   // With two or more tiles per pair, all but the last one or two are taken whole and round-robin (tiles in flight at
@@ -609,7 +629,7 @@ int launch_tc2(const Problem &pr) {
     p.dp_waves = tiles % pairs == 0 ? tiles / pairs : tiles / pairs - 1;
     p.sk_tile0 = p.dp_waves * pairs;
     p.total_iters = (tiles - p.sk_tile0) * p.k_iters;
-    p.m_fast = pick_tile_order(pr.dev, 2.0 * pr.m * pr.k, 0.5 * pr.n * pr.k, p.n_tiles, p.m_tiles, pairs);
+    p.m_fast = pick_tile_order(pr.plan ? -1 : pr.dev, 2.0 * pr.m * pr.k, 0.5 * pr.n * pr.k, p.n_tiles, p.m_tiles, pairs);
   }
   // No whole-tile waves (fewer than two tiles per pair).  Fewer tiles than pairs: as in the single-CTA kernel
   // (pick_workers).  More: a cut in which every pair takes a whole number of half tiles (cuts at tile edges and
@@ -630,6 +650,10 @@ int launch_tc2(const Problem &pr) {
   p.iters_per_cta = p.total_iters > 0 ? (p.total_iters + pairs - 1) / pairs : 1;     // per PAIR
   if (p.dp_waves == 0) pairs = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
   p.workers = pairs;
+  if (pr.plan) {
+    *pr.plan = w4a16_plan_t{W4A16_KERNEL_PAIRS, TM, Cfg::KS, pairs, 2, p.dp_waves, p.total_iters > 0 ? p.iters_per_cta : 0};
+    return W4A16_OK;
+  }
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   Maps mp;   // each CTA of the pair loads half of the tile's activation rows
   if (!get_maps(pr, Cfg::KS, Cfg::HALF_ROWS, GROUPED, OUT == w4a16::OUT_TMA, mp)) return W4A16_ERR_CUDA;
@@ -686,7 +710,7 @@ int dispatch_tc(const Problem &pr) {
   if (pr.m <= 16 && k256 && g_use_decode) {   // the HBM-bound case has a kernel of its own
     // few tiles and no split count from the caller: one cluster per tile
     if (g_use_cluster && pr.sms <= 0 && pr.c_ld == 0 && !pr.orphan_finisher) {
-      const int n_tiles = pr.n / w4a16::TILE_N, nsm = sm_count(pr.dev);
+      const int n_tiles = pr.n / w4a16::TILE_N, nsm = problem_sm_count(pr);
       // the size that fills most SMs; if that many clusters of that size cannot be resident together (a cluster
       // lives inside one GPC), half the size, as long as a quarter of the SMs still gets work and a rank no more than
       // 16 stages (2048 x 8192 at m = 16: 7.5 us on 16 clusters of 4 against 9.7 us on stream-K; 2048 x 28672 with 28
@@ -746,7 +770,7 @@ int dispatch_tc(const Problem &pr) {
   // (an explicit split count from the caller stands in for the 74 pairs of a whole B200)
   // (fewer tiles than pairs: the pairs that pick_workers would put to work)
   const int pair_tiles = (int)((pr.n / 256) * ((pr.m + tm - 1) / tm));
-  int pairs_at_work = pr.sms > 1 ? pr.sms / 2 : 74;
+  int pairs_at_work = pr.sms > 1 ? pr.sms / 2 : (pr.plan ? std::max(pr.plan_sms / 2, 1) : 74);
   if (pr.sms <= 0 && g_aligned_cut && pr.n % 256 == 0 && k128 && pair_tiles <= pairs_at_work)
     pairs_at_work = pick_workers(pair_tiles, pr.k / 128, pairs_at_work, 0.45, 2.2);
   const long pair_stages = (long)pair_tiles * (pr.k / 128) / pairs_at_work;
@@ -870,6 +894,19 @@ extern "C" int w4a16_marlin_gemm(const void *A, const void *B, void *C, const vo
                                  int thread_n, int sms, int max_par) {
   return gemm_entry(false, A, B, C, s, prob_m, prob_n, prob_k, workspace, groupsize, dev,
                     static_cast<cudaStream_t>(stream), thread_k, thread_n, sms, max_par);
+}
+
+extern "C" int w4a16_plan(int prob_m, int prob_n, int prob_k, int groupsize, int sms, int device_sms, w4a16_plan_t *out) {
+  if (!out || device_sms < 2 || device_sms > MAX_GRID || prob_m < 0 || prob_n < 0 || prob_k < 0) return W4A16_ERR_ARG;
+  int thread_k = -1, thread_n = -1;
+  const int chk = check_problem(prob_m, prob_n, prob_k, groupsize, thread_k, thread_n);
+  *out = w4a16_plan_t{W4A16_KERNEL_NONE, 0, 0, 0, 0, 0, 0};
+  if (chk == -1) return W4A16_OK;
+  if (chk != W4A16_OK) return chk;
+  Problem pr{nullptr, nullptr, nullptr, nullptr, prob_m, prob_n, prob_k, groupsize, 0, sms, nullptr};
+  pr.plan = out;
+  pr.plan_sms = device_sms;
+  return dispatch_tc(pr);
 }
 
 // The GEMM with HOST activations and HOST output: copy in, multiply, copy out, all enqueued on `stream`.

@@ -157,6 +157,29 @@ int w4a16_workspace_ints(int prob_n, int max_par);
  * (include/barrier.h:85-96). */
 int w4a16_device_status(int dev, void *stream);
 
+/* Which kernel a call of w4a16_marlin_gemm with these sizes would launch on a device of `device_sms` SMs, and how the
+ * work would be cut.  Pure host arithmetic: no CUDA call, no device needed.  `sms` as in w4a16_marlin_gemm.  Returns
+ * the code that call would return for the sizes (W4A16_OK, or the shape errors); for an empty problem `kernel` is
+ * W4A16_KERNEL_NONE.  The cluster form is planned as if every cluster could be resident at once (the launch itself
+ * asks cudaOccupancyMaxActiveClusters and falls back to smaller clusters or stream-K).  The reference's counterpart
+ * is the dispatch table at the end of its launcher (gemm/marlin_gemm/marlin_cute_kernel.cu:62-115), which is not
+ * callable by itself. */
+#define W4A16_KERNEL_NONE 0
+#define W4A16_KERNEL_SINGLE 1         /* one CTA per worker, stream-K */
+#define W4A16_KERNEL_PAIRS 2          /* one CTA pair per worker (256 weight columns per tile) */
+#define W4A16_KERNEL_DECODE 3         /* prob_m <= 16: one CTA per worker, stream-K or one whole tile each */
+#define W4A16_KERNEL_DECODE_CLUSTER 4 /* prob_m <= 16: one cluster per 128-column tile */
+typedef struct {
+  int kernel;            /* W4A16_KERNEL_* */
+  int tile_rows;         /* batch rows per tile */
+  int k_per_stage;       /* k per pipeline stage */
+  int workers;           /* CTAs (pairs: CTA pairs) launched */
+  int ctas_per_worker;   /* 1, 2 for pairs; for the cluster form the cluster size, `workers` counting CTAs */
+  int whole_tile_waves;  /* pairs: waves of whole tiles before the stream-K part */
+  int stages_per_worker; /* k-stages per worker in the stream-K part (the cluster form: per CTA) */
+} w4a16_plan_t;
+int w4a16_plan(int prob_m, int prob_n, int prob_k, int groupsize, int sms, int device_sms, w4a16_plan_t *out);
+
 /* Frees the scratch and status word the library keeps for (dev, stream), after synchronising `stream`.  No launch
  * captured in a CUDA graph on that stream may be replayed afterwards.  The reference has no counterpart (it owns
  * no memory).  Returns W4A16_OK also when nothing was kept. */

@@ -85,7 +85,8 @@ def test_llama70b_layers_and_their_shards(n_full, k):
     (128, 1024, 4096, "4 pair tiles cut 2 ways: 8 pairs, each inside one tile"),
     (128, 2048, 8192, "8 pair tiles cut 4 ways"),
     (96, 4096, 4096, "16 pair tiles of one ragged batch tile"),
-    (128, 512, 4096, "too few stages per pair: single-CTA kernel, 4 tiles cut evenly"),
+    (128, 512, 4096, "two pair tiles cut 2 ways"),
+    (128, 4096, 512, "too few stages per pair: single-CTA kernel, 32 tiles of 4 stages, one each"),
     (256, 4096, 4096, "two batch tiles of 128 rows, 64 pairs"),
     (576, 12288, 4096, "144 tiles = 2 whole waves on 72 of the 74 pairs, no stream-K part"),
     (200, 4096, 11008, "stage count without a usable divisor: the even cut"),
