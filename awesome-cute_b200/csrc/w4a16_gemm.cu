@@ -306,21 +306,27 @@ const bool g_aligned_cut = [] {
 // workers and batch tiles wider than 16 rows.  The even cut over all workers makes most of them straddle two tiles
 // (contributor to one, finisher of the other) and cuts a tile workers / tiles ways; a cut that lines up with the
 // tiles (every tile cut the same s ways, s a divisor of k_iters, every worker inside one tile) avoids the straddling,
-// and a finisher then folds s - 1 partial tiles through L2.  Both are priced in microseconds, t_stage per stage and
-// t_fix per partial tile folded, and the cheaper one wins.  Measured at m = 128 (single-CTA kernel): 4096 x 4096
+// and a finisher then folds s - 1 partial tiles through L2.  All are priced in microseconds, t_stage per stage and
+// t_fix per partial tile folded, and the cheapest wins.  Measured at m = 128 (single-CTA kernel): 4096 x 4096
 // 17.5 -> 14.9 us (s = 4), 1024 x 4096 27.8 us on the even cut (every tile cut 16 ways).  The two prices were fitted on
 // CTA pairs at m = 128 (us per launch): 2048 x 8192 cut 2 / 4 / 8 ways 19.2 / 16.5 / 19.3, 1024 x 28672 cut 4 / 7 / 8 / 16
 // ways 31.6 / 26.3 / 26.9 / 33.3, 4096 x 4096 cut 2 / 4 ways 13.5 / 14.3, 12288 x 4096 whole tiles on 48 pairs 20.7
 // against 18.8 on the even cut over 74.
 int pick_workers(int tiles, int k_iters, int max_workers, double t_stage, double t_fix) {
+  // Every range length `per` up to a whole tile is a candidate (the even cut over all workers is one of them): the
+  // workers then number ceil(total / per), a tile is cut into ceil(k_iters / per) pieces, and unless `per` divides
+  // k_iters (or there is one tile only) the ranges drift against the tile edges, which costs about one more partial
+  // tile to fold.
   const long total = (long)tiles * k_iters;
-  const int even_per = (int)((total + max_workers - 1) / max_workers);
-  double best = even_per * t_stage + ((double)max_workers / tiles) * t_fix;
+  double best = 0.0;
   int workers = max_workers;
-  for (int s = 1; s <= k_iters && (long)tiles * s <= max_workers; ++s) {
-    if (k_iters % s) continue;
-    const double cost = (k_iters / s) * t_stage + (s - 1) * t_fix;
-    if (cost < best) best = cost, workers = tiles * s;
+  for (int per = 1; per <= k_iters; ++per) {
+    const long w = (total + per - 1) / per;
+    if (w > max_workers) continue;
+    const int pieces = (k_iters + per - 1) / per;
+    const bool lined_up = k_iters % per == 0 || tiles == 1;
+    const double cost = per * t_stage + (pieces - 1 + (lined_up ? 0 : 1)) * t_fix;
+    if (best == 0.0 || cost < best) best = cost, workers = (int)w;
   }
   return workers;
 }
