@@ -363,6 +363,11 @@ int launch_single(const Problem &pr) {
   // of 32-64 rows ~0.5 us)
   if (pr.sms <= 0 && K::TM > 16 && g_aligned_cut && !pr.orphan_finisher && tiles <= grid)
     grid = pick_workers(tiles, p.k_iters, grid, 0.45, K::TM >= 128 ? 2.2 : 0.5);
+  // 16-row tiles outside the whole-tile rule above (very narrow layers: a 128-column layer of 28672 k would be one tile
+  // cut 112 ways, its finisher folding 111 slices three at a time): the same pricing, a stage at 0.36 us and a 16-row
+  // slice at 0.35 us (2048 x 28672 cut 7 / 8 / 9.25 ways: 14.1 / 14.6 / 14.9 us)
+  if (pr.sms <= 0 && K::TM <= 16 && g_aligned_cut && !pr.orphan_finisher && tiles <= grid && grid != tiles)
+    grid = pick_workers(tiles, p.k_iters, grid, 0.36, 0.35);
   p.iters_per_cta = (p.total_iters + grid - 1) / grid;
   grid = (p.total_iters + p.iters_per_cta - 1) / p.iters_per_cta;
   p.s = static_cast<const __half *>(pr.s);

@@ -30,6 +30,9 @@ def test_decode_forms():
     assert plan(16, 8192, 28672)["kernel"] == "decode"
     d = plan(16, 1024, 28672)
     assert (d["kernel"], d["ctas_per_worker"], d["workers"]) == ("decode_cluster", 8, 64)
+    # a very narrow layer is not cut one stage per CTA (one tile 112 ways: 57 us) but into a few long pieces (13 us)
+    d = plan(16, 128, 28672)
+    assert (d["kernel"], d["workers"], d["stages_per_worker"]) == ("decode", 14, 8)
     # k not a multiple of 256: the general kernel with 128-k stages
     d = plan(16, 4096, 4224)
     assert (d["kernel"], d["tile_rows"], d["k_per_stage"]) == ("single", 16, 128)
