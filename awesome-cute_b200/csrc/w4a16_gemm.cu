@@ -296,22 +296,21 @@ struct DecodeKernel {
   static auto kernel() { return w4a16::w4a16_decode_kernel<GROUPED_, OUT_>; }
 };
 
-// W4A16_ALIGNED_CUT=0 in the environment keeps the single-CTA kernel on the even cut over all SMs (A/B timing)
+// W4A16_ALIGNED_CUT=0 in the environment keeps every kernel on the even cut over all workers (A/B timing)
 const bool g_aligned_cut = [] {
   const char *e = std::getenv("W4A16_ALIGNED_CUT");
   return !(e && e[0] == '0');
 }();
 
 // How many workers (CTAs, or CTA pairs) a problem of `tiles` tiles x `k_iters` stages gets when it has fewer tiles than
-// workers and batch tiles wider than 16 rows.  The even cut over all workers makes most of them straddle two tiles
-// (contributor to one, finisher of the other) and cuts a tile workers / tiles ways; a cut that lines up with the
-// tiles (every tile cut the same s ways, s a divisor of k_iters, every worker inside one tile) avoids the straddling,
-// and a finisher then folds s - 1 partial tiles through L2.  All are priced in microseconds, t_stage per stage and
-// t_fix per partial tile folded, and the cheapest wins.  Measured at m = 128 (single-CTA kernel): 4096 x 4096
-// 17.5 -> 14.9 us (s = 4), 1024 x 4096 27.8 us on the even cut (every tile cut 16 ways).  The two prices were fitted on
-// CTA pairs at m = 128 (us per launch): 2048 x 8192 cut 2 / 4 / 8 ways 19.2 / 16.5 / 19.3, 1024 x 28672 cut 4 / 7 / 8 / 16
-// ways 31.6 / 26.3 / 26.9 / 33.3, 4096 x 4096 cut 2 / 4 ways 13.5 / 14.3, 12288 x 4096 whole tiles on 48 pairs 20.7
-// against 18.8 on the even cut over 74.
+// workers.  The even cut over all workers makes most of them straddle two tiles (contributor to one, finisher of the
+// other) and cuts a tile workers / tiles ways, and the finisher of a tile folds every other piece's fp32 partial tile
+// through L2; fewer, longer ranges trade stages per worker against partial tiles to fold.  The candidates are priced
+// in microseconds, t_stage per stage and t_fix per partial tile folded, and the cheapest wins.  Measured at m = 128,
+// us per launch: 4096 x 4096 17.5 on the even cut, 13.4 cut 2 ways; 1024 x 4096 27.8 on the even cut (every tile
+// 16 ways), 12.8 cut 2 ways.  The prices for 128+ rows (0.45, 2.2) were fitted on CTA pairs at m = 128: 2048 x 8192 cut
+// 2 / 4 / 8 ways 19.2 / 16.5 / 19.3, 1024 x 28672 cut 4 / 7 / 8 / 16 ways 31.6 / 26.3 / 26.9 / 33.3, 4096 x 4096 cut 2 / 4
+// ways 13.5 / 14.3, 12288 x 4096 whole tiles on 48 pairs 20.7 against 18.8 on the even cut over 74.
 int pick_workers(int tiles, int k_iters, int max_workers, double t_stage, double t_fix) {
   // Every range length `per` up to a whole tile is a candidate (the even cut over all workers is one of them): the
   // workers then number ceil(total / per), a tile is cut into ceil(k_iters / per) pieces, and unless `per` divides
