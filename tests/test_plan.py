@@ -85,3 +85,39 @@ def test_other_device_sizes_and_refusals():
     assert pkg.plan(16, 4100, 4096)[0] == 1                              # W4A16_ERR_PROB_SHAPE, as the GEMM call
     assert pkg.plan(16, 4096, 4096, 64)[0] == 2                          # W4A16_ERR_KERN_SHAPE: group size 64
     assert pkg.plan(16, 4096, 4096, device_sms=1)[0] == 5                # W4A16_ERR_ARG
+
+
+def test_every_plan_covers_its_problem():
+    """Whatever the launcher chooses, the workers' ranges cover every (tile, k-stage) of the problem, nobody is asked
+    for more workers than the device has, and the tile sizes are ones the kernels are built for.  2000 seeded shapes
+    on three device sizes."""
+    import numpy as np
+    rng = np.random.default_rng(11)
+    for _ in range(2000):
+        m = int(rng.choice([1, 3, 16, 17, 31, 32, 48, 64, 65, 100, 128, 129, 200, 256, 384, 500, 1024, 4096]))
+        n = int(rng.integers(1, 120)) * 256
+        k = int(rng.integers(1, 120)) * 128
+        g = int(rng.choice([128, -1]))
+        sms = int(rng.choice([132, 148, 160]))
+        rc, d = pkg.plan(m, n, k, g, device_sms=sms)
+        assert rc == 0, (m, n, k, g, rc)
+        tm, ks, w, per = d["tile_rows"], d["k_per_stage"], d["workers"], d["stages_per_worker"]
+        assert tm in (16, 32, 64, 128, 192) and ks in (64, 128, 256) and k % ks == 0 and w >= 1, (m, n, k, d)
+        k_iters = k // ks
+        m_tiles = -(-m // tm)
+        if d["kernel"] == "pairs":
+            tiles = n // 256 * m_tiles
+            assert 2 * w <= sms
+            left = tiles - d["whole_tile_waves"] * w
+            assert left >= 0 and w * per >= left * k_iters, (m, n, k, d)
+        elif d["kernel"] == "decode_cluster":
+            tiles = n // 128
+            cl = d["ctas_per_worker"]
+            assert m <= 16 and w == tiles * cl and w <= sms and cl in (2, 4, 8)
+            assert per >= 2 and per * cl <= k_iters < (per + 1) * cl + cl, (m, n, k, d)
+        else:
+            tiles = n // 128 * m_tiles
+            assert d["kernel"] in ("single", "decode") and w <= sms
+            assert (d["kernel"] == "decode") == (m <= 16 and k % 256 == 0)
+            assert w * per >= tiles * k_iters, (m, n, k, d)
+            assert (w - 1) * per < tiles * k_iters, (m, n, k, d)      # no worker without work
